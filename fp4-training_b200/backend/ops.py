@@ -1,0 +1,212 @@
+"""Tensor-level wrappers over the fp4t C ABI.
+
+Outputs are allocated with torch (caching allocator, current device), the kernels run on
+torch's current stream, and nothing here synchronises.  CPU tensors are rejected: there
+is no host implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import SR_HASH, SR_NOISE, SR_NONE  # noqa: F401  (re-exported)
+
+NVFP4_BLOCK = 16
+MXFP8_BLOCK = 32
+
+_status = {}
+LAUNCHES = {"quantize": 0, "gemm": 0, "misc": 0}   # kernels enqueued by this process
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise NotImplementedError("fp4t operators run on CUDA tensors only (no CPU implementation)")
+
+
+def status_word(device) -> torch.Tensor:
+    """Device int32[4] the GEMM kernels write to if one of their bounded waits runs out."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status[key]
+
+
+def check_status(device="cuda") -> None:
+    """Synchronising check of the status word; raises if a kernel gave up on a wait."""
+    s = status_word(device)
+    code = int(s[0].item())
+    if code != 0:
+        s.zero_()
+        raise RuntimeError(f"fp4t GEMM kernel abandoned a wait (role code {code})")
+
+
+def _alloc_q(outer, inner, blk, packed, device):
+    codes = torch.empty((outer, inner // 2 if packed else inner), dtype=torch.uint8, device=device)
+    sf = torch.empty(_lib.sf_shape(outer, inner // blk), dtype=torch.uint8, device=device)
+    return codes, sf
+
+
+def _quantize(fmt, x, want_row, want_t, sr, noise, noise_t, seed):
+    if x.ndim != 2:
+        raise ValueError("Input tensor must be 2D for block quantization")
+    _need_cuda(x, noise, noise_t)
+    blk = NVFP4_BLOCK if fmt == "nvfp4" else MXFP8_BLOCK
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        x = x.to(torch.float32)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, cols = x.shape
+    if want_row and cols % blk:
+        raise ValueError(f"row-wise {fmt} quantization needs columns to be a multiple of {blk}")
+    if want_t and rows % 32:
+        raise ValueError(f"transposed {fmt} quantization needs rows to be a multiple of 32")
+    dev = x.device
+    codes = sf = codes_t = sf_t = None
+    with torch.cuda.device(dev):
+        if want_row:
+            codes, sf = _alloc_q(rows, cols, blk, fmt == "nvfp4", dev)
+        if want_t:
+            codes_t, sf_t = _alloc_q(cols, rows, blk, fmt == "nvfp4", dev)
+        if rows == 0 or cols == 0:
+            return codes, sf, codes_t, sf_t
+        L = _lib.lib()
+        if fmt == "nvfp4":
+            if noise is not None:
+                noise = noise.to(torch.float32).reshape(rows, cols).contiguous()
+            if noise_t is not None:
+                noise_t = noise_t.to(torch.float32).reshape(cols, rows).contiguous()
+            rc = L.fp4t_quantize_nvfp4(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                       _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                                       int(sr), _lib.ptr(noise), _lib.ptr(noise_t),
+                                       ctypes.c_uint64(seed & (2 ** 64 - 1)), _lib.stream_ptr(dev))
+            _lib.check(rc, "fp4t_quantize_nvfp4")
+        else:
+            rc = L.fp4t_quantize_mxfp8(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                       _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                                       _lib.stream_ptr(dev))
+            _lib.check(rc, "fp4t_quantize_mxfp8")
+        LAUNCHES["quantize"] += 1
+    return codes, sf, codes_t, sf_t
+
+
+def quantize_nvfp4(x, want_row=True, want_t=False, sr=SR_NONE, noise=None, noise_t=None, seed=0):
+    """-> (codes [R, C/2], sf, codes_t [C, R/2], sf_t); entries not requested are None."""
+    return _quantize("nvfp4", x, want_row, want_t, sr, noise, noise_t, seed)
+
+
+def quantize_mxfp8(x, want_row=True, want_t=False):
+    """-> (codes [R, C], sf, codes_t [C, R], sf_t); entries not requested are None."""
+    return _quantize("mxfp8", x, want_row, want_t, SR_NONE, None, None, 0)
+
+
+def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None):
+    _need_cuda(p_codes, p_sf, q_codes, q_sf, bias)
+    rows, cols = p_codes.shape[0], q_codes.shape[0]
+    kbytes = p_codes.shape[1]
+    if q_codes.shape[1] != kbytes:
+        raise RuntimeError(f"Mismatch matmul inner: P has {kbytes} code bytes per row, Q has {q_codes.shape[1]}")
+    k = kbytes * 2 if fmt == "nvfp4" else kbytes
+    dev = p_codes.device
+    if bias is not None:
+        if bias.ndim != 1 or bias.shape[0] != cols:
+            raise RuntimeError(f"bias is expected to be 1D of length {cols}, but got shape {tuple(bias.shape)}")
+        bias = bias.to(torch.bfloat16).contiguous()
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+        if rows == 0 or cols == 0:
+            return out
+        fn = _lib.lib().fp4t_gemm_nvfp4 if fmt == "nvfp4" else _lib.lib().fp4t_gemm_mxfp8
+        rc = fn(_lib.ptr(p_codes), _lib.ptr(p_sf), _lib.ptr(q_codes), _lib.ptr(q_sf), _lib.ptr(bias),
+                _lib.ptr(out), _lib.dtype_code(out.dtype), out.stride(0), rows, cols, k,
+                _lib.ptr(status_word(dev)), _lib.stream_ptr(dev))
+        _lib.check(rc, f"fp4t_gemm_{fmt}")
+        LAUNCHES["gemm"] += 1
+    return out
+
+
+def gemm_nvfp4(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None):
+    """D[rows, cols] = P . Q^T (+bias); P/Q packed E2M1 codes [outer, K/2]."""
+    return _gemm("nvfp4", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out)
+
+
+def gemm_mxfp8(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None):
+    """D[rows, cols] = P . Q^T (+bias); P/Q E4M3 codes [outer, K]."""
+    return _gemm("mxfp8", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out)
+
+
+def pack_e2m1(values: torch.Tensor) -> torch.Tensor:
+    """fp32/bf16 values on the E2M1 grid [R, C] -> packed codes [R, C/2]."""
+    _need_cuda(values)
+    values = values.contiguous()
+    rows, cols = values.shape
+    out = torch.empty((rows, cols // 2), dtype=torch.uint8, device=values.device)
+    with torch.cuda.device(values.device):
+        rc = _lib.lib().fp4t_pack_e2m1(_lib.ptr(values), _lib.dtype_code(values.dtype), _lib.ptr(out), rows, cols,
+                                       _lib.stream_ptr(values.device))
+        _lib.check(rc, "fp4t_pack_e2m1")
+        LAUNCHES["misc"] += 1
+    return out
+
+
+def unpack_e2m1(codes: torch.Tensor) -> torch.Tensor:
+    """packed codes [R, C/2] -> fp32 values [R, C]."""
+    _need_cuda(codes)
+    codes = codes.contiguous()
+    rows, half = codes.shape
+    out = torch.empty((rows, half * 2), dtype=torch.float32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        rc = _lib.lib().fp4t_unpack_e2m1(_lib.ptr(codes), _lib.ptr(out), rows, half * 2,
+                                         _lib.stream_ptr(codes.device))
+        _lib.check(rc, "fp4t_unpack_e2m1")
+        LAUNCHES["misc"] += 1
+    return out
+
+
+def _relayout(fn_name, src, outer, inner):
+    _need_cuda(src)
+    src = src.contiguous()
+    shape = _lib.sf_shape(outer, inner)
+    if fn_name == "fp4t_swizzle_colwise":   # the reference returns [ceil(inner/4)*32, ceil(outer/128)*16]
+        shape = ((inner + 3) // 4 * 32, (outer + 127) // 128 * 16)
+    out = torch.empty(shape, dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        fn = getattr(_lib.lib(), fn_name)
+        if fn_name == "fp4t_swizzle_rowwise":
+            rc = fn(_lib.ptr(src), _lib.ptr(out), outer, inner, _lib.stream_ptr(src.device))
+        else:
+            rc = fn(_lib.ptr(src), _lib.ptr(out), inner, outer, _lib.stream_ptr(src.device))
+        _lib.check(rc, fn_name)
+        LAUNCHES["misc"] += 1
+    return out
+
+
+def swizzle_rowwise(scale: torch.Tensor) -> torch.Tensor:
+    """logical [outer, inner] bytes -> canonical 128x4 tile layout."""
+    return _relayout("fp4t_swizzle_rowwise", scale, scale.shape[0], scale.shape[1])
+
+
+def swizzle_colwise(scale: torch.Tensor) -> torch.Tensor:
+    """logical [inner, outer] bytes -> the reference's column-wise layout."""
+    return _relayout("fp4t_swizzle_colwise", scale, scale.shape[1], scale.shape[0])
+
+
+def colwise_to_canonical(sw: torch.Tensor, inner: int, outer: int) -> torch.Tensor:
+    """Reference column-wise layout of a logical [inner, outer] matrix -> canonical tiles of its transpose."""
+    return _relayout("fp4t_unswizzle_colwise_to_rowwise", sw, outer, inner)
+
+
+def transpose_bytes(src: torch.Tensor) -> torch.Tensor:
+    _need_cuda(src)
+    src = src.contiguous()
+    rows, cols = src.shape
+    out = torch.empty((cols, rows), dtype=torch.uint8, device=src.device)
+    with torch.cuda.device(src.device):
+        rc = _lib.lib().fp4t_transpose_bytes(_lib.ptr(src), _lib.ptr(out), rows, cols, _lib.stream_ptr(src.device))
+        _lib.check(rc, "fp4t_transpose_bytes")
+        LAUNCHES["misc"] += 1
+    return out

@@ -1,0 +1,154 @@
+// Shared host/device helpers of the fp4t library: error reporting, number-format
+// conversions and the scale-factor tile addressing used by every kernel.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+#include "../../include/fp4t.h"
+
+namespace fp4t {
+
+// Thread-local error text behind fp4t_last_error().
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define FP4T_REQUIRE(cond, ...)            \
+  do {                                     \
+    if (!(cond)) {                         \
+      ::fp4t::set_error(__VA_ARGS__);      \
+      return FP4T_ERR_ARG;                 \
+    }                                      \
+  } while (0)
+
+#define FP4T_CUDA(call)                                        \
+  do {                                                         \
+    cudaError_t e_ = (call);                                   \
+    if (e_ != cudaSuccess) return ::fp4t::cuda_fail(e_, #call); \
+  } while (0)
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Byte offset of scale (outer o, k-block i) in the 128x4 tile layout with `ntx`
+// tiles along the k-block axis.
+__host__ __device__ __forceinline__ int64_t sf_offset(int64_t o, int64_t i, int64_t ntx) {
+  return ((o >> 7) * ntx + (i >> 2)) * 512 + (o & 31) * 16 + ((o & 127) >> 5) * 4 + (i & 3);
+}
+
+// Offset inside one 512-byte tile.
+__device__ __forceinline__ int sf_tile_offset(int o, int i) {
+  return (o & 31) * 16 + ((o & 127) >> 5) * 4 + (i & 3);
+}
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t hi16_in_low) {
+  return __uint_as_float(hi16_in_low << 16);
+}
+
+// Eight fp32 values -> eight E2M1 codes in one 32-bit word, element j in nibble j.
+// Round to nearest even, saturate to +-6, sign bit kept (so -0.0f -> 0x8).
+__device__ __forceinline__ uint32_t cvt_e2m1x8(float v0, float v1, float v2, float v3,
+                                               float v4, float v5, float v6, float v7) {
+  uint32_t out;
+  asm("{\n\t"
+      ".reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t"
+      "}"
+      : "=r"(out)
+      : "f"(v0), "f"(v1), "f"(v2), "f"(v3), "f"(v4), "f"(v5), "f"(v6), "f"(v7));
+  return out;
+}
+
+// Two fp32 values -> one byte of E2M1 codes (lo in bits 0..3).
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+  uint32_t out;
+  asm("{\n\t"
+      ".reg .b8 b0;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.u32.u8 %0, b0;\n\t"
+      "}"
+      : "=r"(out)
+      : "f"(lo), "f"(hi));
+  return out;
+}
+
+// fp32 in [2^-9, 448] -> E4M3 byte, round to nearest even.
+__device__ __forceinline__ uint32_t cvt_e4m3(float v) {
+  return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// NVFP4 block scale from the block's amax: clamp(amax / 6, 2^-9, 448) with a true division.
+__device__ __forceinline__ float nvfp4_scale(float amax) {
+  return fminf(fmaxf(__fdiv_rn(amax, 6.0f), 0x1p-9f), 448.0f);
+}
+
+// x / s rounded to nearest, computed as a reciprocal multiply plus one FMA correction.
+// With r = RN(1/s) this returns RN(x/s) for every bf16 x and every scale derived from a
+// bf16 amax (checked exhaustively on the host); -0.0f comes out as +0.0f.
+__device__ __forceinline__ float div_corrected(float x, float s, float r) {
+  float q = x * r;
+  float rem = fmaf(-q, s, x);
+  return fmaf(rem, r, q);
+}
+
+// Stochastic E2M1 rounding of y with u in [0,1):
+//   e = clamp(floor(log2|y|), 0, 2), m = |y| / 2^e, r = rint(2m + (u - 0.5)),
+//   q = sign(y) * 2^e * (r / 2)          (a later RNE+saturate conversion clips 8 to 6)
+__device__ __forceinline__ float sr_round(float y, float u) {
+  float a = fabsf(y);
+  float p2 = a >= 4.0f ? 4.0f : (a >= 2.0f ? 2.0f : 1.0f);
+  float inv = a >= 4.0f ? 0.25f : (a >= 2.0f ? 0.5f : 1.0f);
+  float m = a * inv;
+  float r = rintf(fmaf(m, 2.0f, u - 0.5f)) * 0.5f;
+  float sgn = y > 0.0f ? 1.0f : (y < 0.0f ? -1.0f : 0.0f);
+  return (sgn * p2) * r;
+}
+
+// Counter-based uniform in [0,1) with 24 random bits from (seed, index).
+__device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t idx) {
+  uint32_t h = (uint32_t)idx * 0x9E3779B1u ^ (uint32_t)seed;
+  h ^= (uint32_t)(idx >> 32) * 0x85EBCA77u + (uint32_t)(seed >> 32);
+  h ^= h >> 16; h *= 0x85EBCA6Bu;
+  h ^= h >> 13; h *= 0xC2B2AE35u;
+  h ^= h >> 16;
+  return (float)(h >> 8) * 0x1p-24f;
+}
+
+// MXFP8: E8M0 byte of a block from its amax (floor(log2 amax) - 8 + 127, clamped at 0).
+__device__ __forceinline__ uint32_t mx_scale_byte(float amax) {
+  int e8 = (int)(__float_as_uint(amax) >> 23) & 0xFF;
+  int b = e8 - 8;
+  return (uint32_t)(b < 0 ? 0 : b);
+}
+// Multiplier 2^-(byte-127) that maps block elements into the E4M3 range.
+__device__ __forceinline__ float mx_inv_scale(uint32_t byte) {
+  return __uint_as_float((254u - byte) << 23);
+}
+
+// y -> E4M3 byte. Three mantissa bits, ties away from zero, denormals kept (grid 2^-9),
+// saturating at +-448.
+template <bool kHalfAway>
+__device__ __forceinline__ uint32_t mx_e4m3_byte(float y) {
+  if (!kHalfAway) {
+    return (uint32_t)__nv_cvt_float_to_fp8(y + 0.0f, __NV_SATFINITE, __NV_E4M3);
+  }
+  uint32_t sign = y < 0.0f ? 0x80u : 0u;  // sign(0) is 0: -0.0f encodes as +0
+  float a = fabsf(y);
+  bool den = a < 0x1p-6f;
+  float a2 = den ? a + 0x1p-6f : a;
+  uint32_t b = (__float_as_uint(a2) + 0x00080000u) >> 20;
+  int v = (int)b - (den ? (121 << 3) : (120 << 3));
+  v = v > 0x7E ? 0x7E : v;
+  return (uint32_t)v | sign;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace fp4t

@@ -1,0 +1,164 @@
+// Error reporting and the small byte-level operators of the C ABI: FP4 pack / unpack,
+// scale-matrix re-layouts and a byte transpose.  All are HBM-bound copies with index
+// arithmetic; they exist for operand forms the reference's op signatures accept and the
+// fused quantizers do not already produce.
+#include <cstdarg>
+#include <cstdio>
+
+#include "fp4t_common.cuh"
+
+namespace fp4t {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+  return FP4T_ERR_CUDA;
+}
+
+namespace {
+
+inline int grid_for(int64_t items, int threads) {
+  const int64_t b = ceil_div(items, threads);
+  return (int)(b > 148 * 32 ? 148 * 32 : (b < 1 ? 1 : b));
+}
+
+template <typename TIn>
+__global__ void pack_e2m1_kernel(const TIn* __restrict__ v, uint8_t* __restrict__ codes, int64_t nbytes) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    codes[i] = (uint8_t)cvt_e2m1x2((float)v[2 * i], (float)v[2 * i + 1]);
+  }
+}
+
+__global__ void unpack_e2m1_kernel(const uint8_t* __restrict__ codes, float* __restrict__ v, int64_t nbytes) {
+  const float grid[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t b = codes[i];
+    const float lo = grid[b & 7], hi = grid[(b >> 4) & 7];
+    v[2 * i] = (b & 8) ? -lo : lo;
+    v[2 * i + 1] = (b & 0x80) ? -hi : hi;
+  }
+}
+
+// mode 0: logical [outer, inner]      -> canonical tiles
+// mode 1: logical [inner, outer]      -> reference column-wise layout
+// mode 2: reference column-wise bytes -> canonical tiles of the transpose
+__global__ void sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                   int64_t outer, int64_t inner, int mode) {
+  const int64_t ntx_k = (inner + 3) / 4;        // tiles along k-blocks
+  const int64_t nt_o = (outer + 127) / 128;     // tiles along outer
+  const int64_t total = outer * inner;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t o, i;
+    if (mode == 0) { o = e / inner; i = e % inner; } else { i = e / outer; o = e % outer; }
+    const int64_t canon = sf_offset(o, i, ntx_k);
+    const int64_t refcol = ((i >> 2) * 32 + (o & 31)) * (nt_o * 16) + (o >> 7) * 16 + ((o & 127) >> 5) * 4 + (i & 3);
+    if (mode == 0) dst[canon] = src[e];
+    else if (mode == 1) dst[refcol] = src[e];
+    else dst[canon] = src[refcol];
+  }
+}
+
+__global__ void transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                       int64_t rows, int64_t cols) {
+  __shared__ uint8_t t[64][65];
+  const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+  for (int j = threadIdx.y; j < 64; j += blockDim.y) {
+    const int64_t r = r0 + j, c = c0 + threadIdx.x;
+    t[j][threadIdx.x] = (r < rows && c < cols) ? src[r * cols + c] : (uint8_t)0;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 64; j += blockDim.y) {
+    const int64_t c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) dst[c * rows + r] = t[threadIdx.x][j];
+  }
+}
+
+int sf_relayout(const void* src, void* dst, int64_t outer, int64_t inner, int mode, cudaStream_t stream,
+                const char* name) {
+  FP4T_REQUIRE(src && dst, "%s: null pointer", name);
+  FP4T_REQUIRE(outer >= 0 && inner >= 0, "%s: negative size", name);
+  if (outer == 0 || inner == 0) return FP4T_OK;
+  FP4T_CUDA(cudaMemsetAsync(dst, 0, (size_t)fp4t_sf_bytes(outer, inner), stream));
+  sf_relayout_kernel<<<grid_for(outer * inner, 256), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), outer, inner, mode);
+  FP4T_CUDA(cudaGetLastError());
+  return FP4T_OK;
+}
+
+}  // namespace
+}  // namespace fp4t
+
+using namespace fp4t;
+
+extern "C" const char* fp4t_last_error(void) { return fp4t::g_error; }
+extern "C" int fp4t_version(void) { return 100; }
+
+extern "C" int64_t fp4t_sf_bytes(int64_t outer, int64_t kblocks) {
+  if (outer <= 0 || kblocks <= 0) return 0;
+  return ceil_div(outer, 128) * ceil_div(kblocks, 4) * 512;
+}
+
+extern "C" int fp4t_pack_e2m1(const void* values, int in_dtype, void* codes, int64_t rows, int64_t cols,
+                              fp4t_stream_t stream) {
+  FP4T_REQUIRE(values && codes, "fp4t_pack_e2m1: null pointer");
+  FP4T_REQUIRE(rows >= 0 && cols >= 0 && cols % 2 == 0, "fp4t_pack_e2m1: cols must be even (cols=%lld)", (long long)cols);
+  FP4T_REQUIRE(in_dtype == FP4T_DT_F32 || in_dtype == FP4T_DT_BF16, "fp4t_pack_e2m1: bad dtype");
+  const int64_t nbytes = rows * cols / 2;
+  if (nbytes == 0) return FP4T_OK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (in_dtype == FP4T_DT_F32)
+    pack_e2m1_kernel<float><<<grid_for(nbytes, 256), 256, 0, s>>>(static_cast<const float*>(values), static_cast<uint8_t*>(codes), nbytes);
+  else
+    pack_e2m1_kernel<__nv_bfloat16><<<grid_for(nbytes, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(values), static_cast<uint8_t*>(codes), nbytes);
+  FP4T_CUDA(cudaGetLastError());
+  return FP4T_OK;
+}
+
+extern "C" int fp4t_unpack_e2m1(const void* codes, float* values, int64_t rows, int64_t cols,
+                                fp4t_stream_t stream) {
+  FP4T_REQUIRE(values && codes, "fp4t_unpack_e2m1: null pointer");
+  FP4T_REQUIRE(rows >= 0 && cols >= 0 && cols % 2 == 0, "fp4t_unpack_e2m1: cols must be even");
+  const int64_t nbytes = rows * cols / 2;
+  if (nbytes == 0) return FP4T_OK;
+  unpack_e2m1_kernel<<<grid_for(nbytes, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(codes), values, nbytes);
+  FP4T_CUDA(cudaGetLastError());
+  return FP4T_OK;
+}
+
+extern "C" int fp4t_swizzle_rowwise(const void* logical, void* dst, int64_t outer, int64_t inner,
+                                    fp4t_stream_t stream) {
+  return sf_relayout(logical, dst, outer, inner, 0, reinterpret_cast<cudaStream_t>(stream), "fp4t_swizzle_rowwise");
+}
+extern "C" int fp4t_swizzle_colwise(const void* logical, void* dst, int64_t inner, int64_t outer,
+                                    fp4t_stream_t stream) {
+  return sf_relayout(logical, dst, outer, inner, 1, reinterpret_cast<cudaStream_t>(stream), "fp4t_swizzle_colwise");
+}
+extern "C" int fp4t_unswizzle_colwise_to_rowwise(const void* src, void* dst, int64_t inner, int64_t outer,
+                                                 fp4t_stream_t stream) {
+  return sf_relayout(src, dst, outer, inner, 2, reinterpret_cast<cudaStream_t>(stream), "fp4t_unswizzle_colwise_to_rowwise");
+}
+
+extern "C" int fp4t_transpose_bytes(const void* src, void* dst, int64_t rows, int64_t cols,
+                                    fp4t_stream_t stream) {
+  FP4T_REQUIRE(src && dst, "fp4t_transpose_bytes: null pointer");
+  FP4T_REQUIRE(rows >= 0 && cols >= 0, "fp4t_transpose_bytes: negative size");
+  if (rows == 0 || cols == 0) return FP4T_OK;
+  const dim3 grid((unsigned)ceil_div(cols, 64), (unsigned)ceil_div(rows, 64));
+  FP4T_REQUIRE(grid.y <= 65535u, "fp4t_transpose_bytes: rows too large");
+  transpose_bytes_kernel<<<grid, dim3(64, 4), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, cols);
+  FP4T_CUDA(cudaGetLastError());
+  return FP4T_OK;
+}

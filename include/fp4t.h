@@ -1,0 +1,160 @@
+/*
+ * fp4t -- C ABI of the B200 (sm_100a) quantized-linear training path.
+ *
+ * One shared library, plain pointers and sizes.  Every entry point
+ *   - takes DEVICE pointers owned by the caller (unless a parameter says "host"),
+ *   - enqueues its kernels on the given CUDA stream and returns without
+ *     synchronising,
+ *   - allocates nothing, creates no stream and keeps no reference to caller memory,
+ *   - returns FP4T_OK (0) or a negative FP4T_ERR_* code; the text of the last
+ *     error on the calling thread is available from fp4t_last_error().
+ *
+ * Layout conventions (identical to what the reference hands to cuBLASLt):
+ *   - NVFP4 codes: E2M1, two per byte, element 2j in bits 0..3 and element 2j+1
+ *     in bits 4..7 of byte j of a row; rows are contiguous, [outer, K/2] bytes.
+ *   - MXFP8 codes: E4M3 bytes, [outer, K].
+ *   - Scale factors: one byte per block of 16 (NVFP4, UE4M3) or 32 (MXFP8,
+ *     UE8M0) elements along K, stored in the 128x4 tile layout: for the logical
+ *     matrix [outer, kblocks] the byte of (o, i) sits at
+ *        ((o/128) * ceil(kblocks/4) + i/4) * 512 + (o%32)*16 + ((o%128)/32)*4 + i%4
+ *     and the buffer is zero padded to whole 512-byte tiles
+ *     (fp4t_sf_bytes() gives its size).
+ *
+ * "Replaces" comments cite the reference project (vuiseng9/fp4-training) by
+ * file:line within that project.
+ */
+#ifndef FP4T_H_
+#define FP4T_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FP4T_API __attribute__((visibility("default")))
+#else
+#define FP4T_API
+#endif
+
+typedef struct CUstream_st* fp4t_stream_t; /* a cudaStream_t / CUstream */
+
+enum {
+  FP4T_OK = 0,
+  FP4T_ERR_ARG = -1,      /* bad pointer, size, alignment or enum value            */
+  FP4T_ERR_CUDA = -2,     /* a CUDA runtime / driver call failed                   */
+  FP4T_ERR_UNSUPPORTED = -3, /* valid request that this build does not implement   */
+  FP4T_ERR_DEVICE = -4    /* the device is not an sm_100 part                      */
+};
+
+enum { FP4T_DT_BF16 = 0, FP4T_DT_F32 = 1 };
+
+/* Stochastic rounding of NVFP4 codes. */
+enum {
+  FP4T_SR_NONE = 0,   /* round to nearest even                                      */
+  FP4T_SR_NOISE = 1,  /* u ~ U[0,1) read from caller tensors (bit-exact parity mode) */
+  FP4T_SR_HASH = 2    /* u generated in the kernel from (seed, element index)        */
+};
+
+/* Operand layout selector of the reference op signature (custom/linear/cublaslt.py:14-17). */
+enum { FP4T_TN = 0, FP4T_NN = 1, FP4T_NT = 2 };
+
+FP4T_API const char* fp4t_last_error(void);
+FP4T_API int fp4t_version(void);
+
+/* Bytes of the swizzled scale buffer for a logical [outer, kblocks] scale matrix. */
+FP4T_API int64_t fp4t_sf_bytes(int64_t outer, int64_t kblocks);
+
+/*
+ * Fused NVFP4 quantizer: reads x [rows, cols] (row-major, leading dimension ld
+ * elements) ONCE and writes any of
+ *   codes   [rows, cols/2], sf   = swizzled scales of logical [rows, cols/16]
+ *   codes_t [cols, rows/2], sf_t = swizzled scales of logical [cols, rows/16]
+ * (the second pair is the quantization of x transposed, 1x16 blocks along rows).
+ * A null codes/codes_t pointer skips that output.  Per-tensor scale is 1.
+ * sr_mode FP4T_SR_NOISE reads noise [rows, cols] and noise_t [cols, rows] (fp32).
+ * Requirements: cols % 16 == 0 for the row-wise output, rows % 32 == 0 for the
+ * transposed one; bf16 input additionally wants x and ld 16-byte aligned
+ * (otherwise a slower generic kernel is used).
+ *
+ * Replaces custom/quantize.py:57-122 (quantize_nvfp4, q_nvfp4_rowwise), the
+ * transposes at custom/linear/nvfp4.py:59,74-75, the scale swizzle at
+ * custom/swizzle.py:6-23 and the FP4 pack kernel at
+ * custom/backend/csrc/cublaslt_mm_nvfp4.cu:145-166,275-306.
+ */
+FP4T_API int fp4t_quantize_nvfp4(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                        void* codes, void* sf, void* codes_t, void* sf_t,
+                        int sr_mode, const float* noise, const float* noise_t, uint64_t seed,
+                        fp4t_stream_t stream);
+
+/*
+ * Fused MXFP8 quantizer, same shape contract with 1x32 blocks:
+ *   codes   [rows, cols]   sf   ~ logical [rows, cols/32]
+ *   codes_t [cols, rows]   sf_t ~ logical [cols, rows/32]
+ * Requirements: cols % 32 == 0 (row-wise), rows % 32 == 0 (transposed).
+ *
+ * Replaces custom/quantize.py:8-49 (q_mxfp8_rowwise / q_mxfp8_colwise through
+ * microxcaling's quantize_mx_op) and custom/swizzle.py:6-60.
+ */
+FP4T_API int fp4t_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                        void* codes, void* sf, void* codes_t, void* sf_t,
+                        fp4t_stream_t stream);
+
+/*
+ * Block-scaled GEMMs on tcgen05:  D[rows, cols] = P[rows, K] . Q[cols, K]^T (+ bias[cols]),
+ * fp32 accumulation in tensor memory, D written as bf16 or fp32 (row-major,
+ * leading dimension ldd elements).  P/Q are code matrices, p_sf/q_sf their
+ * swizzled scales; bias is bf16 or null.
+ * Requirements: NVFP4 K % 32 == 0, MXFP8 K % 16 == 0; code pointers 16-byte aligned;
+ * scale pointers 16-byte aligned; ldd*sizeof(elem) % 16 == 0.
+ *
+ * Replaces custom/backend/csrc/cublaslt_mm_nvfp4.cu:184-448 and
+ * custom/backend/csrc/cublaslt_mm_mxfp8.cu:103-320 (mode TN; P is the binding's
+ * B argument, Q its A argument, D its Dt[n, m]).
+ * status, when not null, is a device int32[4] the kernel writes a nonzero code
+ * into if one of its bounded waits ran out (0 otherwise left untouched).
+ */
+FP4T_API int fp4t_gemm_nvfp4(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                    const void* bias_bf16, void* d, int d_dtype, int64_t ldd,
+                    int64_t rows, int64_t cols, int64_t k, int32_t* status,
+                    fp4t_stream_t stream);
+FP4T_API int fp4t_gemm_mxfp8(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                    const void* bias_bf16, void* d, int d_dtype, int64_t ldd,
+                    int64_t rows, int64_t cols, int64_t k, int32_t* status,
+                    fp4t_stream_t stream);
+
+/*
+ * fp32 values that already lie on the E2M1 grid -> packed codes (RNE, saturate
+ * to +-6) and back.  Replaces pack_rowwise_to_2xfp4,
+ * custom/backend/csrc/cublaslt_mm_nvfp4.cu:109-182.  in_dtype selects fp32/bf16 input.
+ */
+FP4T_API int fp4t_pack_e2m1(const void* values, int in_dtype, void* codes, int64_t rows, int64_t cols,
+                   fp4t_stream_t stream);
+FP4T_API int fp4t_unpack_e2m1(const void* codes, float* values, int64_t rows, int64_t cols,
+                     fp4t_stream_t stream);
+
+/*
+ * Scale-matrix re-layouts on bytes.
+ *  fp4t_swizzle_rowwise: logical [outer, inner] -> 128x4 tile layout (custom/swizzle.py:6-23).
+ *  fp4t_swizzle_colwise: logical [inner, outer] -> the layout of custom/swizzle.py:43-60.
+ *  fp4t_unswizzle_colwise_to_rowwise: bytes in the layout of custom/swizzle.py:43-60 for a
+ *    logical [inner, outer] matrix -> canonical tile layout of its transpose [outer, inner].
+ * dst must hold fp4t_sf_bytes(outer, inner) bytes.
+ */
+FP4T_API int fp4t_swizzle_rowwise(const void* logical, void* dst, int64_t outer, int64_t inner,
+                         fp4t_stream_t stream);
+FP4T_API int fp4t_swizzle_colwise(const void* logical, void* dst, int64_t inner, int64_t outer,
+                         fp4t_stream_t stream);
+FP4T_API int fp4t_unswizzle_colwise_to_rowwise(const void* src, void* dst, int64_t inner, int64_t outer,
+                                      fp4t_stream_t stream);
+
+/* Byte-matrix transpose [rows, cols] -> [cols, rows] (E4M3 codes for the NN / NT operand
+ * forms of custom/backend/csrc/cublaslt_mm_mxfp8.cu:70-88). */
+FP4T_API int fp4t_transpose_bytes(const void* src, void* dst, int64_t rows, int64_t cols,
+                         fp4t_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP4T_H_ */

@@ -268,7 +268,7 @@ def mxfp8_quantize_rowwise(x: torch.Tensor):
     else:
         t = torch.round(t)
     q = (t / (2.0 ** MX_E4M3_MBITS) * torch.pow(2.0, pe)).clamp(max=E4M3_NORM_MAX)
-    q = torch.where(torch.signbit(y), -q, q)
+    q = torch.where(y < 0, -q, q)                 # sign(0) = 0, so -0.0 encodes as +0
     codes = q.reshape(r, c).to(torch.float8_e4m3fn).view(torch.uint8)
     sbytes = (sexp.squeeze(-1) + 127.0).to(torch.uint8)
     return codes, sbytes
