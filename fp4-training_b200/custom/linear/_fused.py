@@ -1,0 +1,63 @@
+"""Fused operand preparation shared by the quantized Linear autograd functions.
+
+The reference quantizes each GEMM operand separately and materialises bf16 transposes
+first (custom/linear/nvfp4.py:59,74-75; custom/linear/mxfp8.py:59-80).  Here each of X, W
+and dY is read once by one kernel that emits the row-wise operand and the transposed
+operand together, so a linear layer's forward+backward is three quantizer launches and
+three GEMM launches.
+"""
+from __future__ import annotations
+
+import os
+from functools import partial
+
+import torch
+
+from backend import ops as _ops
+
+from .. import quantize as Q
+
+
+def parity_mode() -> bool:
+    """FP4T_PARITY=1: stochastic-rounding noise comes from `torch.rand`, drawn with the
+    shapes and in the order of the reference (dgrad operand first, then wgrad operand),
+    instead of the in-kernel generator."""
+    return os.environ.get("FP4T_PARITY", "0") == "1"
+
+
+def is_stock(quant, expected) -> bool:
+    """True when the module's quantizer table still holds the stock entries, i.e. the fused
+    kernels compute exactly what the table describes."""
+    if quant is None or list(quant.keys()) != list(expected.keys()):
+        return False
+    for k, want in expected.items():
+        got = quant[k]
+        if isinstance(want, partial):
+            if not (isinstance(got, partial) and got.func is want.func and got.keywords == want.keywords):
+                return False
+        elif got is not want:
+            return False
+    return True
+
+
+def quant_pair(fmt, t, want_row, want_t, sr=False):
+    """(codes, sf, codes_t, sf_t) of tensor t in format fmt ('nvfp4' | 'mxfp8')."""
+    if fmt == "mxfp8":
+        return Q.mxfp8_fused(t, want_row, want_t)
+    if not sr:
+        return Q.nvfp4_fused(t, want_row, want_t)
+    if parity_mode():
+        r, c = t.shape
+        noise = torch.rand(r, c // 16, 16, device=t.device) if want_row else None
+        noise_t = torch.rand(c, r // 16, 16, device=t.device) if want_t else None
+        return Q.nvfp4_fused(t, want_row, want_t, sr=True, noise=noise, noise_t=noise_t)
+    return Q.nvfp4_fused(t, want_row, want_t, sr=True)
+
+
+def gemm(fmt, p, p_sf, q, q_sf, bias, out_dtype):
+    fn = _ops.gemm_nvfp4 if fmt == "nvfp4" else _ops.gemm_mxfp8
+    return fn(p, p_sf, q, q_sf, bias, out_dtype)
+
+
+def can_transpose(t) -> bool:
+    return t.shape[0] % 32 == 0

@@ -1,0 +1,108 @@
+"""NVFP4 linear layer: E2M1 codes with UE4M3 scales per 16 elements in all three GEMMs,
+stochastic rounding on the gradient operand (reference: custom/linear/nvfp4.py:17-127)."""
+from collections import OrderedDict
+from functools import partial
+
+import torch
+from torch.amp import custom_bwd, custom_fwd
+
+import backend.xops  # noqa: F401
+
+from ..quantize import q_nvfp4_rowwise
+from . import _fused as F
+from .cublaslt import TransAB
+from .custom import CustomLinear, flatten_apply
+
+op = torch.ops.xops
+
+STOCK = OrderedDict([
+    ('1A', q_nvfp4_rowwise), ('1B', q_nvfp4_rowwise),
+    ('2A', q_nvfp4_rowwise), ('2B', partial(q_nvfp4_rowwise, sr=True)),
+    ('3A', q_nvfp4_rowwise), ('3B', partial(q_nvfp4_rowwise, sr=True)),
+])
+
+
+class Nvfp4Matmul(torch.autograd.Function):
+    """Y = X W^T + b, dX = dY W, dW = dY^T X with every operand in NVFP4.
+
+    With the stock quantizer table the fused path runs: X, W (forward) and dY (backward)
+    are each quantized once into both operand forms.  A customised table falls back to the
+    reference's own sequence of calls (custom/linear/nvfp4.py:25-90): bf16 transposes, one
+    quantizer call per operand and the packing `xops.cublaslt_mm_nvfp4` operator."""
+
+    @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx, X, W, b, quant: OrderedDict):
+        ctx.quant = quant
+        ctx.has_bias = b is not None
+        ctx.fused = F.is_stock(quant, STOCK)
+        if not ctx.fused:
+            Wq, sW = quant['1A'](W)
+            Xq, sX = quant['1B'](X)
+            Y, _ = op.cublaslt_mm_nvfp4(TransAB.TN.value, X.dtype, Wq, sW, Xq, sX, b)
+            ctx.save_for_backward(X, W)
+            return Y
+        if X.ndim != 2 or W.ndim != 2:
+            raise ValueError("Input tensor must be 2D for nvfp4 quantization")
+        X = X.contiguous()
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        Wc, Wsf, Wtc, Wtsf = F.quant_pair("nvfp4", W, True, need_dx and F.can_transpose(W))
+        Xc, Xsf, Xtc, Xtsf = F.quant_pair("nvfp4", X, True, need_dw and F.can_transpose(X))
+        Y = F.gemm("nvfp4", Xc, Xsf, Wc, Wsf, b, X.dtype)
+        # operands of the backward GEMMs; the bf16 tensor is kept only where the transposed
+        # form could not be built (the backward pass then reports the shape error)
+        ctx.save_for_backward(Wtc, Wtsf, Xtc, Xtsf,
+                              W if (need_dx and Wtc is None) else None,
+                              X if (need_dw and Xtc is None) else None)
+        return Y
+
+    @staticmethod
+    @custom_bwd(device_type="cuda")
+    def backward(ctx, grad_Y):
+        grad_Y = grad_Y.contiguous()
+        grad_X = grad_W = grad_b = None
+        if not ctx.fused:
+            X, W = ctx.saved_tensors
+            if ctx.needs_input_grad[0]:
+                Wtq, sWt = ctx.quant['2A'](W.to(grad_Y.dtype).T.contiguous())
+                Gq, sG = ctx.quant['2B'](grad_Y)
+                grad_X, _ = op.cublaslt_mm_nvfp4(TransAB.TN.value, grad_Y.dtype, Wtq, sWt, Gq, sG, None)
+            if ctx.needs_input_grad[1]:
+                Xtq, sXt = ctx.quant['3A'](X.to(grad_Y.dtype).T.contiguous())
+                Gtq, sGt = ctx.quant['3B'](grad_Y.T.contiguous())
+                grad_W, _ = op.cublaslt_mm_nvfp4(TransAB.TN.value, grad_Y.dtype, Xtq, sXt, Gtq, sGt, None)
+        else:
+            Wtc, Wtsf, Xtc, Xtsf, W, X = ctx.saved_tensors
+            need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+            if need_dx and Wtc is None:
+                _, _, Wtc, Wtsf = F.quant_pair("nvfp4", W, False, True)
+            if need_dw and Xtc is None:
+                _, _, Xtc, Xtsf = F.quant_pair("nvfp4", X, False, True)
+            Gc, Gsf, Gtc, Gtsf = F.quant_pair("nvfp4", grad_Y, need_dx, need_dw, sr=True)
+            if need_dx:
+                grad_X = F.gemm("nvfp4", Gc, Gsf, Wtc, Wtsf, None, grad_Y.dtype)
+            if need_dw:
+                grad_W = F.gemm("nvfp4", Gtc, Gtsf, Xtc, Xtsf, None, grad_Y.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            grad_b = grad_Y.sum(dim=0)
+        return grad_X, grad_W, grad_b, None
+
+
+class CublasltNvfp4Linear(CustomLinear):
+    """`nn.Linear` drop-in whose three GEMMs run in NVFP4 on tcgen05."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._init_quantizers()
+
+    @classmethod
+    def from_linear(cls, linear_layer):
+        linear = super().from_linear(linear_layer)
+        linear._init_quantizers()
+        return linear
+
+    def _init_quantizers(self):
+        self.quantizers = OrderedDict(STOCK)   # all row-wise: every GEMM is K-major on both sides
+
+    def forward(self, input):
+        return flatten_apply(self, Nvfp4Matmul.apply, input, self.quantizers)

@@ -1,0 +1,79 @@
+"""Pre-LN transformer block whose six projections come from the `linear_impl` recipe
+switch (reference: models/transformer_block.py:16-106)."""
+import torch.nn.functional as F
+from torch import nn
+
+from custom import (
+    AddmmLinear,
+    CublasltFwdNvfp4BwdMxfp8Linear,
+    CublasltLinear,
+    CublasltMxfp8Linear,
+    CublasltNvfp4Linear,
+    CustomLinear,
+)
+
+LINEAR_IMPL = {
+    "torch": nn.Linear,
+    "custom_py": CustomLinear,
+    "custom_aten": AddmmLinear,
+    "cublaslt": CublasltLinear,
+    "cublaslt_mxfp8": CublasltMxfp8Linear,
+    "cublaslt_nvfp4": CublasltNvfp4Linear,
+    "cublaslt_nvf4_fw_mxf8_bw": CublasltFwdNvfp4BwdMxfp8Linear,
+}
+
+REF_IMPL = ["torch", "custom_py", "custom_aten", "cublaslt", "cublaslt_mxfp8", "cublaslt_nvfp4",
+            "cublaslt_nvf4_fw_mxf8_bw"]
+
+
+class AttentionBlock(nn.Module):
+    """x + o_proj(softmax(q k^T * attn_scale) v).  As in the reference
+    (models/transformer_block.py:74,95) attn_scale is 1 / dh**-0.5, i.e. the scores are
+    MULTIPLIED by sqrt(dh); loss-curve parity depends on keeping that."""
+
+    def __init__(self, E, H, dropout=0.1, impl="torch"):
+        super().__init__()
+        assert E % H == 0, "head size is not multiple of embedding size"
+        self.E, self.H, self.dh = E, H, E // H
+        self.attn_scale = 1 / (self.dh ** -0.5)
+        self.preln = nn.LayerNorm(E)
+        linear = LINEAR_IMPL[impl]
+        self.q_proj = linear(E, E)
+        self.k_proj = linear(E, E)
+        self.v_proj = linear(E, E)
+        self.o_proj = linear(E, E)
+        self.dropout = nn.Dropout(dropout)
+
+    def forward(self, x):
+        B, L, E = x.shape
+        residual = x
+        x = self.preln(x)
+        q = self.q_proj(x).view(B, L, self.H, self.dh).transpose(1, 2)
+        k_t = self.k_proj(x).view(B, L, self.H, self.dh).transpose(1, 2).transpose(-2, -1)
+        v = self.v_proj(x).view(B, L, self.H, self.dh).transpose(1, 2)
+        prob = self.dropout(F.softmax((q @ k_t) * self.attn_scale, dim=-1))
+        attn = (prob @ v).transpose(1, 2).contiguous().view(B, L, E)
+        return residual + self.o_proj(attn)
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, E, F, H, dropout=0.1, impl="torch"):
+        super().__init__()
+        self.E, self.F, self.H, self.impl = E, F, H, impl
+        self.attn = AttentionBlock(E, H, dropout, impl=impl)
+        linear = LINEAR_IMPL[impl]
+        self.ffn = nn.ModuleDict({
+            "preln": nn.LayerNorm(E),
+            "up_proj": linear(E, F),
+            "act": nn.GELU(),
+            "act_dropout": nn.Dropout(dropout),
+            "down_proj": linear(F, E),
+            "dropout": nn.Dropout(dropout),
+        })
+
+    def forward(self, x):
+        hidden = self.attn(x)
+        residual = hidden           # the FFN residual is the attention output
+        for layer in self.ffn.values():
+            hidden = layer(hidden)
+        return residual + hidden

@@ -317,8 +317,8 @@ def gemm_dequant_fp32(p_deq: torch.Tensor, q_deq: torch.Tensor, bias: torch.Tens
 
 
 def rel_frobenius(a: torch.Tensor, ref: torch.Tensor) -> float:
-    a = a.double()
-    ref = ref.double()
+    a = a.detach().double()
+    ref = ref.detach().double()
     return float((a - ref).norm() / ref.norm().clamp_min(1e-300))
 
 
