@@ -2,6 +2,7 @@
 // conversions and the scale-factor tile addressing used by every kernel.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -30,6 +31,19 @@ int cuda_fail(cudaError_t e, const char* what);
   } while (0)
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Number of SMs of the current device, or -1 if it is not an sm_100 part.
+int sm_count();
+
+// 2-D tiled tensor map over a row-major matrix [outer, inner] of `dtype` elements whose rows
+// are row_pitch_bytes apart; out-of-range parts of a box read as zero.
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
+                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
+                         CUtensorMapSwizzle swizzle);
+
+// Device status word used by kernels whose entry point has no status parameter
+// (set per host thread with fp4t_set_status_word, may be null).
+int32_t* current_status_word();
 
 // Byte offset of scale (outer o, k-block i) in the 128x4 tile layout with `ntx`
 // tiles along the k-block axis.
@@ -89,6 +103,42 @@ __device__ __forceinline__ float nvfp4_scale(float amax) {
   return fminf(fmaxf(__fdiv_rn(amax, 6.0f), 0x1p-9f), 448.0f);
 }
 
+// Table form of the same scale for an amax that came from bf16 (7 mantissa bits): entry m
+// holds RN((1 + m/128) / 6) and its correctly rounded reciprocal; the power of two of amax
+// is applied by adding to / subtracting from the exponent field.  Gives the same s as
+// nvfp4_scale and r = RN(1/s) for every finite non-negative bf16 amax (checked exhaustively
+// on the host), without any division.
+struct ScalePair { float s, r; };
+struct ScaleTable { ScalePair v[128]; };
+constexpr ScaleTable make_scale_table() {
+  ScaleTable t{};
+  for (int m = 0; m < 128; ++m) {
+    const float s = (1.0f + (float)m / 128.0f) / 6.0f;
+    t.v[m].s = s;
+    t.v[m].r = 1.0f / s;
+  }
+  return t;
+}
+__device__ __forceinline__ void nvfp4_scale_from_table(const float2* __restrict__ tab, float amax, float& s,
+                                                       float& r) {
+  const uint32_t b = __float_as_uint(amax);
+  const float2 t = tab[(b >> 16) & 0x7Fu];
+  const uint32_t e = (b & 0x7F800000u) - 0x3F800000u;
+  const float sf = __uint_as_float(__float_as_uint(t.x) + e);
+  const float rf = __uint_as_float(__float_as_uint(t.y) - e);
+  const bool lo = (b < 0x0C800000u) || (sf < 0x1p-9f);
+  const bool hi = sf > 448.0f;
+  s = lo ? 0x1p-9f : (hi ? 448.0f : sf);
+  r = lo ? 512.0f : (hi ? (1.0f / 448.0f) : rf);
+}
+// UE4M3 byte of a scale in [2^-9, 448], round to nearest even, integer / FMA pipes only.
+__device__ __forceinline__ uint32_t e4m3_byte_of_scale(float s) {
+  const uint32_t den = __float_as_uint(fmaf(s, 512.0f, 12582912.0f)) & 0xFu;   // multiples of 2^-9
+  const uint32_t b = __float_as_uint(s);
+  const uint32_t nrm = ((b + 0x7FFFFu + ((b >> 20) & 1u)) >> 20) - (120u << 3);
+  return s < 0x1p-6f ? den : nrm;
+}
+
 // x / s rounded to nearest, computed as a reciprocal multiply plus one FMA correction.
 // With r = RN(1/s) this returns RN(x/s) for every bf16 x and every scale derived from a
 // bf16 amax (checked exhaustively on the host); -0.0f comes out as +0.0f.
@@ -109,6 +159,71 @@ __device__ __forceinline__ float sr_round(float y, float u) {
   float r = rintf(fmaf(m, 2.0f, u - 0.5f)) * 0.5f;
   float sgn = y > 0.0f ? 1.0f : (y < 0.0f ? -1.0f : 0.0f);
   return (sgn * p2) * r;
+}
+
+// ---- packed fp32 pairs (FFMA2 / FMUL2 on sm_100) --------------------------------------
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// The two bf16 halves of a 32-bit word as a packed fp32 pair (low half first).
+__device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t w) {
+  return pack2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+// Packed form of div_corrected: x / s for two lanes, rcp = RN(1/s), neg_s = -s.
+__device__ __forceinline__ uint64_t div_corrected2(uint64_t x, uint64_t neg_s, uint64_t rcp) {
+  const uint64_t q = mul2(x, rcp);
+  const uint64_t rem = fma2(q, neg_s, x);
+  return fma2(rem, rcp, q);
+}
+
+// 32-bit integer mix (two multiply-xorshift rounds).
+__device__ __forceinline__ uint32_t mix32(uint32_t h) {
+  h ^= h >> 16; h *= 0x7FEB352Du;
+  h ^= h >> 15; h *= 0x846CA68Bu;
+  h ^= h >> 16;
+  return h;
+}
+
+// Stochastic rounding of y onto the E2M1 grid with 16 random bits: the grid keeps one
+// mantissa bit (after lifting [0,1) to [1,2)), so adding uniform bits below that bit and
+// truncating rounds up with probability equal to the discarded fraction.  Same distribution
+// as sr_round, a fraction of the instructions; results above 6 are clipped by the conversion.
+__device__ __forceinline__ float sr_round_bits(float y, uint32_t r16) {
+  const float a = fabsf(y);
+  const bool small = a < 1.0f;
+  const float t = small ? a + 1.0f : a;
+  const uint32_t b = (__float_as_uint(t) + (r16 << 6)) & 0xFFC00000u;
+  float q = __uint_as_float(b);
+  q = small ? q - 1.0f : q;
+  return copysignf(q, y);
+}
+
+// MXFP8 element conversion for values that came from bf16 (at most 8 significant bits):
+// setting the lowest fp32 mantissa bit moves exact ties off the tie, so the hardware's
+// round-to-nearest-even conversion lands where ties-away-from-zero would.  y0 / y1 must
+// already be +0 for zero inputs.
+__device__ __forceinline__ uint32_t mx_e4m3x2_from_bf16(float y0, float y1) {
+  const float a = __uint_as_float(__float_as_uint(y0) | 1u);
+  const float b = __uint_as_float(__float_as_uint(y1) | 1u);
+  uint32_t out;
+  asm("{\n\t.reg .b16 h;\n\tcvt.rn.satfinite.e4m3x2.f32 h, %2, %1;\n\tcvt.u32.u16 %0, h;\n\t}"
+      : "=r"(out) : "f"(a), "f"(b));
+  return out;
 }
 
 // Counter-based uniform in [0,1) with 24 random bits from (seed, index).

@@ -23,6 +23,65 @@ int cuda_fail(cudaError_t e, const char* what) {
   return FP4T_ERR_CUDA;
 }
 
+static thread_local int32_t* g_status_word = nullptr;
+int32_t* current_status_word() { return g_status_word; }
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0, major = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cached[dev] = (major == 10 && n > 0) ? n : -1;
+  }
+  return cached[dev];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  }
+  return fn;
+}
+
+int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
+                         uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
+                         CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return FP4T_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_pitch_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu outer=%llu pitch=%llu box=%ux%u)", (int)r,
+              (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)row_pitch_bytes, box_inner,
+              box_outer);
+    return FP4T_ERR_CUDA;
+  }
+  return FP4T_OK;
+}
+
 namespace {
 
 inline int grid_for(int64_t items, int threads) {
@@ -102,7 +161,12 @@ int sf_relayout(const void* src, void* dst, int64_t outer, int64_t inner, int mo
 using namespace fp4t;
 
 extern "C" const char* fp4t_last_error(void) { return fp4t::g_error; }
-extern "C" int fp4t_version(void) { return 100; }
+extern "C" int fp4t_version(void) { return 101; }
+
+extern "C" int fp4t_set_status_word(int32_t* device_word) {
+  fp4t::g_status_word = device_word;
+  return FP4T_OK;
+}
 
 extern "C" int64_t fp4t_sf_bytes(int64_t outer, int64_t kblocks) {
   if (outer <= 0 || kblocks <= 0) return 0;

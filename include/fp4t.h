@@ -63,6 +63,14 @@ enum { FP4T_TN = 0, FP4T_NN = 1, FP4T_NT = 2 };
 FP4T_API const char* fp4t_last_error(void);
 FP4T_API int fp4t_version(void);
 
+/*
+ * Device int32[4] that kernels launched afterwards from this host thread write a nonzero
+ * code into if one of their bounded waits runs out (entry points with their own `status`
+ * parameter prefer that one).  Null switches the reporting off.  The caller owns the
+ * memory and zeroes it.
+ */
+FP4T_API int fp4t_set_status_word(int32_t* device_word);
+
 /* Bytes of the swizzled scale buffer for a logical [outer, kblocks] scale matrix. */
 FP4T_API int64_t fp4t_sf_bytes(int64_t outer, int64_t kblocks);
 
