@@ -61,6 +61,10 @@ static EncodeTiledFn get_encode_fn() {
 int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
                          uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
                          CUtensorMapSwizzle swizzle) {
+  // The encode call goes to the driver directly and needs a current context.  A thread that
+  // has made no runtime call yet (e.g. an autograd worker on device 0) has none bound; any
+  // runtime call binds the primary context of the current device.
+  FP4T_CUDA(cudaFree(nullptr));
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from the driver");
