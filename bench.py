@@ -42,6 +42,11 @@ FLOP_PER_STEP = 6.0 * N * IC * OC
 # (0.5 B each) and two scale copies (1/16 B each) out, per element
 QUANT_BYTES = (2.0 + 2 * 0.5 + 2.0 / 16) * (N * IC + OC * IC + N * OC)
 FP4_NOMINAL_TFLOPS = 9000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised
+# under profiles/ (fprop GEMM; quantizer of X).  Both working sets fit the 126 MB L2, so part
+# of the written data had not reached DRAM when the kernel ended.
+GEMM_DRAM_TRAFFIC = {"bytes": 43.7e6, "launch": "fprop 8192x4096x4096", "algorithmic_bytes": 94.4e6 / 3 + 67.1e6}
+QUANT_DRAM_TRAFFIC = {"bytes": 71.4e6, "launch": "X 8192x4096 row+transposed", "algorithmic_bytes": 3.125 * N * IC}
 METRIC = "nvfp4_linear_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 WORKLOAD = "nvfp4_linear_fwd_bwd N=8192 IC=OC=4096 bf16 (quantize x3 + fprop/dgrad/wgrad)"
@@ -75,7 +80,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -181,37 +186,39 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         s[1] = sets[0][1]          # weights are shared state, only the batch changes
     bias = sets[0][3]
     ev = torch.cuda.Event
+    # weight / bias gradients land in two rotating buffers so that the NCCL all-reduce of step i
+    # (on a side stream) can overlap the kernels of step i+1, as it does under the backward
+    # pass of the previous layer in data-parallel training
+    dw_bufs = [torch.empty(OC, IC, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    comm_done = [None, None]
 
-    def hot_step(i, marks=None):
+    def hot_step(i):
         x, w, g, _ = sets[i % nsets]
-
-        def mark(name):
-            if marks is not None:
-                e = ev(enable_timing=True)
-                e.record()
-                marks.append((name, e))
-        mark("start")
         wc, wsf, wtc, wtsf = ops.quantize_nvfp4(w, True, True)
-        mark("quant_w")
         xc, xsf, xtc, xtsf = ops.quantize_nvfp4(x, True, True)
-        mark("quant_x")
         y = ops.gemm_nvfp4(xc, xsf, wc, wsf, bias, torch.bfloat16)
-        mark("fprop")
         gc, gsf, gtc, gtsf = ops.quantize_nvfp4(g, True, True, sr=ops.SR_HASH, seed=i)
-        mark("quant_g")
         dx = ops.gemm_nvfp4(gc, gsf, wtc, wtsf, None, torch.bfloat16)
-        mark("dgrad")
-        dw = ops.gemm_nvfp4(gtc, gtsf, xtc, xtsf, None, torch.bfloat16)
-        mark("wgrad")
+        slot = i % 2
+        if comm_done[slot] is not None:
+            torch.cuda.current_stream().wait_event(comm_done[slot])   # buffer free again
+        dw = ops.gemm_nvfp4(gtc, gtsf, xtc, xtsf, None, torch.bfloat16, out=dw_bufs[slot])
         db = g.sum(dim=0)
-        mark("bias_grad")
         if world > 1:
-            dist.all_reduce(dw)
-            dist.all_reduce(db)
-            mark("allreduce")
+            ready = ev()
+            ready.record()
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(ready)
+                db.record_stream(comm_stream)
+                dist.all_reduce(dw)
+                dist.all_reduce(db)
+                comm_done[slot] = ev()
+                comm_done[slot].record()
         return y, dx, dw, db
 
     def barrier():
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -234,19 +241,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     launches = sum(ops.LAUNCHES.values()) - sum(launches0.values())
     ops.check_status(dev)
 
-    # instrumented pass: per-kernel CUDA-event durations over the same number of steps
-    per = {}
-    for i in range(args.steps):
-        marks = []
-        hot_step(i, marks)
-        torch.cuda.synchronize()
-        for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
-            per.setdefault(name, []).append(a.elapsed_time(b))
-    clocks = sampler.stop() if rank == 0 else None
-    kern_ms = {k: sum(v) / len(v) for k, v in per.items()}
+    # per-kernel durations: each kernel of the step launched back to back between two CUDA
+    # events (events between the kernels of a live step would time launch gaps instead)
+    kern_ms = time_kernels(ops, sets[0], bias, max(10, min(args.steps, 50)))
 
     # end-to-end through the module API with host buffers
     e2e_ms, h2d, d2h = run_e2e(args, dev, rank, world)
+    clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([ms_total, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -283,12 +284,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                      "achieved": gemm_tflops, "peak": fp4_peak, "unit": UNIT, "frac": gemm_tflops / fp4_peak,
                      "peak_basis": f"4 x {peaks['source']} sustained bf16 cuBLAS TFLOP/s (FP4:BF16 dense ratio); "
                                    f"nominal dense FP4 is {FP4_NOMINAL_TFLOPS:.0f}",
-                     "frac_of_nominal": gemm_tflops / FP4_NOMINAL_TFLOPS, "traffic": None,
+                     "frac_of_nominal": gemm_tflops / FP4_NOMINAL_TFLOPS, "traffic": GEMM_DRAM_TRAFFIC,
                      "ms_per_launch": gemm_ms / 3},
-        "roofline_quantize": {"bound": "hbm", "kernel": "quantize_tile_kernel<nvfp4> (X, W, dY)",
+        "roofline_quantize": {"bound": "hbm", "kernel": "quantize_tma_kernel<nvfp4> (X, W, dY)",
                               "achieved": quant_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                               "frac": quant_gbs / peaks["hbm_gbs"], "peak_basis": f"{peaks['source']} copy bandwidth",
-                              "traffic": None, "ms_per_launch": quant_ms / 3},
+                              "traffic": QUANT_DRAM_TRAFFIC, "ms_per_launch": quant_ms / 3},
         "kernel_ms": kern_ms,
         "e2e": {"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
@@ -299,6 +300,65 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
+
+
+def kernel_closures(ops, inputs, bias):
+    """The seven launches of one step as standalone closures over prepared operands."""
+    x, w, g, _ = inputs
+    wc, wsf, wtc, wtsf = ops.quantize_nvfp4(w, True, True)
+    xc, xsf, xtc, xtsf = ops.quantize_nvfp4(x, True, True)
+    gc, gsf, gtc, gtsf = ops.quantize_nvfp4(g, True, True, sr=ops.SR_HASH, seed=1)
+    y = torch.empty(N, OC, dtype=torch.bfloat16, device=x.device)
+    dx = torch.empty(N, IC, dtype=torch.bfloat16, device=x.device)
+    dw = torch.empty(OC, IC, dtype=torch.bfloat16, device=x.device)
+    return {
+        "quant_w": lambda: ops.quantize_nvfp4(w, True, True),
+        "quant_x": lambda: ops.quantize_nvfp4(x, True, True),
+        "quant_g": lambda: ops.quantize_nvfp4(g, True, True, sr=ops.SR_HASH, seed=1),
+        "fprop": lambda: ops.gemm_nvfp4(xc, xsf, wc, wsf, bias, torch.bfloat16, out=y),
+        "dgrad": lambda: ops.gemm_nvfp4(gc, gsf, wtc, wtsf, None, torch.bfloat16, out=dx),
+        "wgrad": lambda: ops.gemm_nvfp4(gtc, gtsf, xtc, xtsf, None, torch.bfloat16, out=dw),
+        "bias_grad": lambda: g.sum(dim=0),
+    }
+
+
+def time_kernels(ops, inputs, bias, reps, only=None):
+    out = {}
+    for name, fn in kernel_closures(ops, inputs, bias).items():
+        if only is not None and name != only:
+            continue
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = a.elapsed_time(b) / reps
+    return out
+
+
+def run_single_kernel(args):
+    """--kernel NAME: launch one kernel of the step --steps times (after --warmup launches).
+    This is the small command the ncu captures under profiles/ were taken with."""
+    from backend import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    inputs = synth_inputs(N, IC, OC, 0, dev)
+    fn = kernel_closures(ops, inputs, inputs[3])[args.kernel]
+    for _ in range(args.warmup):
+        fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(args.steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    print(json.dumps({"kernel": args.kernel, "launches": args.steps, "ms_per_launch": a.elapsed_time(b) / args.steps}))
 
 
 def run_e2e(args, dev, rank, world):
@@ -351,10 +411,13 @@ def run_e2e(args, dev, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default=None,
+                    choices=["quant_w", "quant_x", "quant_g", "fprop", "dgrad", "wgrad", "bias_grad"],
+                    help="run only this kernel of the step (profiling aid); no benchmark line")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -367,6 +430,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    if args.kernel is not None:
+        run_single_kernel(args)
+        return
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
