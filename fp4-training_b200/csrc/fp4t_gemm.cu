@@ -7,25 +7,33 @@
 // in the 128x4 tile layout, which is exactly the 32-lane x 16-byte image that one
 // `tcgen05.cp ... 32x128b.warpx4` drops into tensor memory for the MMA to consume.
 //
-// Kernel structure (one persistent CTA per SM, 256 threads, static tile schedule):
-//   warp 0     TMA producer: per stage one 128-byte-of-K slab of P (128 rows) and of Q
-//              (kBN rows) with 128-byte swizzle, plus the matching scale tiles as plain
-//              bulk copies (they are contiguous in the tile layout).  No multicast.
-//   warp 1     MMA issuer: scale tiles shared memory -> tensor memory (tcgen05.cp), then
-//              four tcgen05.mma per stage (K = 64 FP4 / 32 FP8 elements each) accumulating
-//              into a 128 x kBN fp32 tile in tensor memory; tcgen05.commit releases the
-//              stage and, after the last stage, publishes the accumulator.
-//   warp 2     tensor-memory allocation / release.
-//   warps 4-7  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, + bias, convert,
-//              16-byte stores.  Two accumulators alternate so the epilogue of tile i
-//              overlaps the main loop of tile i+1; with kBN = 256 the two accumulators
-//              overlap by 48 columns (the scale factors need the rest) and the epilogue
-//              drains the shared columns first, then signals the MMA warp early.
+// One-CTA kernel (one persistent CTA per SM, 384 threads, static tile schedule):
+//   warp 0      TMA producer: per stage one 128-byte-of-K slab of P (128 rows) and of Q
+//               (kBN rows) with 128-byte swizzle, plus the matching scale tiles (tensor maps
+//               over the tile layout; K beyond the matrix reads as zero codes and zero
+//               scales).  No multicast.
+//   warp 1      MMA issuer: four tcgen05.mma per stage (K = 64 FP4 / 32 FP8 elements each)
+//               into a 128 x kBN fp32 accumulator in tensor memory; tcgen05.commit releases
+//               the stage and, after the last stage, publishes the accumulator.
+//   warp 2      tensor-memory allocation / release.
+//   warps 4-7   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, + bias, convert,
+//               16-byte stores.  Two accumulators alternate so the epilogue of tile i
+//               overlaps the main loop of tile i+1; with kBN = 256 they overlap by 96 columns
+//               (the scale factors need the rest); the epilogue pulls those columns into
+//               registers first and signals the MMA warp before it converts and stores.
+//   warps 8-11  scale factors: each warp copies the stage's scale tiles from shared memory
+//               into its 32-lane quadrant of tensor memory with tcgen05.st (two buffers), so
+//               the tensor pipe executes nothing but MMAs.  (tcgen05.cp does the same copy
+//               inside the tensor pipe, in order with the MMAs; twelve of them per NVFP4
+//               stage cost more pipe time than the four MMAs.)
+// Two-CTA kernel: see below.
 //
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records a code in the
 // caller's status word, stops issuing work, lets copies in flight land and releases its
 // tensor memory before returning.
 #include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
 
 #include "fp4t_common.cuh"
 #include "fp4t_ptx.cuh"
@@ -40,6 +48,8 @@ constexpr int kGemmThreads = 256;
 constexpr int kTmemCols = 512;
 constexpr int kSfTmemBase = 464;     // scale factors live in the last 48 columns
 
+constexpr int kGemm1Threads = 384;
+
 template <int kFmt, int kBN>
 struct Cfg {
   static constexpr int kSfChunks = kFmt == kNvfp4 ? 4 : 1;   // 512-byte scale tiles per 128 rows per stage
@@ -49,15 +59,18 @@ struct Cfg {
   static constexpr int kSfaBytes = kSfChunks * 512;
   static constexpr int kSfbBytes = kOuterB * kSfChunks * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = (kBN == 256) ? 4 : 6;
+  static constexpr int kStages = (220 * 1024) / kStageBytes > 8 ? 8 : (220 * 1024) / kStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr int kAccStride = (kBN == 256) ? 208 : 128;  // column distance of the two accumulators
+  // tensor memory: accumulators at 0 and kAccStride, two 48-column scale-factor buffers at 416 and 464
+  static constexpr int kAccStride = (kBN == 256) ? 160 : 128;
   static constexpr int kChunks = kBN / 32;                     // 32-column epilogue chunks
-  static constexpr int kEarlyChunks = (kBN == 256) ? 2 : kChunks;  // chunks drained before the MMA may go on
-  static constexpr int kSfaCol = kSfTmemBase;
-  static constexpr int kSfbCol = kSfTmemBase + 16;
+  static constexpr int kEarlyChunks = (kBN == 256) ? 3 : 0;    // chunks the other accumulator overlaps
+  static constexpr int kSfBuf0 = 416;
+  static constexpr int kSfBufStride = 48;
+  static constexpr int kSfbOff = 16;                           // SFB columns follow the 16 SFA columns
+  static constexpr int kSfBoxElems = kSfChunks * 64;           // 8-byte words per scale box row
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-  static_assert(kAccStride + kBN <= kSfTmemBase, "tensor memory budget");
+  static_assert(kAccStride + kBN <= kSfBuf0, "tensor memory budget");
 };
 
 struct GemmParams {
@@ -138,12 +151,108 @@ __device__ __forceinline__ uint32_t make_idesc() {
   return (fmt << 7) | (fmt << 10) | ((uint32_t)(kBN >> 3) << 17) | (sfmt << 23) | ((uint32_t)(kBM >> 4) << 24);
 }
 
+// Epilogue of one 32-column chunk held in registers: + bias, convert, store (16-byte vectors
+// when the row pitch and the chunk allow it, element-wise at ragged edges).
+__device__ __forceinline__ void store_chunk(const GemmParams& g, const int row, const bool row_ok, const int col0,
+                                            const uint32_t (&r)[32]) {
+  if (row_ok && col0 < g.cols) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (g.bias != nullptr) {
+      if (g.vec_ok && col0 + 32 <= g.cols) {
+        const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint4 b = __ldg(bp + q4);
+          const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[q4 * 8 + 2 * j] += __uint_as_float(bw[j] << 16);
+            v[q4 * 8 + 2 * j + 1] += __uint_as_float(bw[j] & 0xFFFF0000u);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < g.cols) v[j] += __bfloat162float(g.bias[col0 + j]);
+      }
+    }
+    if (g.out_f32) {
+      float* dp = static_cast<float*>(g.d) + (int64_t)row * g.ldd + col0;
+      if (g.vec_ok && col0 + 32 <= g.cols) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          reinterpret_cast<float4*>(dp)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < g.cols) dp[j] = v[j];
+      }
+    } else {
+      __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(g.d) + (int64_t)row * g.ldd + col0;
+      if (g.vec_ok && col0 + 32 <= g.cols) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t w[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+            w[t] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          reinterpret_cast<uint4*>(dp)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < g.cols) dp[j] = __float2bfloat16_rn(v[j]);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // The kernel
 // ------------------------------------------------------------------------------------
+__device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// N consecutive 32-bit columns of this warp's lane quadrant from registers (N = 4, 8, 16 or 32).
+template <int N>
+__device__ __forceinline__ void tc_st_n(uint32_t taddr, const uint32_t (&v)[N]) {
+  static_assert(N == 4 || N == 8 || N == 16 || N == 32, "unsupported width");
+  if constexpr (N == 4) {
+    tc_st4(taddr, v[0], v[1], v[2], v[3]);
+  } else if constexpr (N == 8) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+  } else if constexpr (N == 16) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+        "%15, %16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+        "%15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+        "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+        "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+  }
+}
+
 template <int kFmt, int kBN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemm1Threads, 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                        const __grid_constant__ CUtensorMap map_psf, const __grid_constant__ CUtensorMap map_qsf,
                         const GemmParams g) {
   using C = Cfg<kFmt, kBN>;
   extern __shared__ uint8_t smem_raw[];
@@ -152,11 +261,12 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 
   // barrier block sits after the stages
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kStages * C::kStageBytes);
-  const uint32_t bar_full = smem_u32(bars);                       // [kStages]
-  const uint32_t bar_empty = bar_full + 8 * C::kStages;           // [kStages]
-  const uint32_t bar_tmem_full = bar_empty + 8 * C::kStages;      // [1]
+  const uint32_t bar_full = smem_u32(bars);                       // [kStages] stage data landed
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;           // [kStages] MMAs that read the stage are done
+  const uint32_t bar_sf_ready = bar_empty + 8 * C::kStages;       // [2] scale factors are in tensor memory
+  const uint32_t bar_tmem_full = bar_sf_ready + 16;               // [1]
   const uint32_t bar_tmem_empty = bar_tmem_full + 8;              // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -167,6 +277,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
+    mbar_init(bar_sf_ready, 4);
+    mbar_init(bar_sf_ready + 8, 4);
     mbar_init(bar_tmem_full, 1);
     mbar_init(bar_tmem_empty, 4);
     *abort_flag = 0;
@@ -195,31 +307,22 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m_idx = tile / g.n_tiles, n_idx = tile % g.n_tiles;
-      int outer_b = g.q_outer - n_idx * C::kOuterB;
-      outer_b = outer_b > C::kOuterB ? C::kOuterB : outer_b;
-      const uint8_t* sfa_g = g.p_sf + (int64_t)m_idx * g.ntx * 512;
-      const uint8_t* sfb_g = g.q_sf + (int64_t)(n_idx * C::kOuterB) * g.ntx * 512;
-      const int64_t sfb_outer_stride = (int64_t)g.ntx * 512;
       const int row_p = m_idx * kBM, row_q = n_idx * kBN;
       for (int ks = 0; ks < g.k_stages; ++ks) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 1)) { ok = false; break; }
-        int nchunk = g.ntx - ks * C::kSfChunks;
-        nchunk = nchunk > C::kSfChunks ? C::kSfChunks : nchunk;
-        const uint32_t sf_bytes = (uint32_t)nchunk * 512u;
         const uint32_t a_s = smem_base + stage * C::kStageBytes;
         const uint32_t b_s = a_s + C::kABytes;
         const uint32_t sfa_s = b_s + C::kBBytes;
         const uint32_t sfb_s = sfa_s + C::kSfaBytes;
         const uint32_t bar = bar_full + 8 * stage;
-        mbar_expect_tx(bar, (uint32_t)(C::kABytes + C::kBBytes) + sf_bytes * (uint32_t)(1 + outer_b));
+        mbar_expect_tx(bar, (uint32_t)C::kStageBytes);
+        tma_load_2d(sfa_s, &map_psf, bar, ks * C::kSfBoxElems, m_idx);
+#pragma unroll
+        for (int o = 0; o < C::kOuterB; ++o) {
+          tma_load_2d(sfb_s + o * C::kSfaBytes, &map_qsf, bar, ks * C::kSfBoxElems, n_idx * C::kOuterB + o);
+        }
         tma_load_2d(a_s, &map_p, bar, ks * 128, row_p);
         tma_load_2d(b_s, &map_q, bar, ks * 128, row_q);
-        bulk_load(sfa_s, sfa_g, sf_bytes, bar);
-        for (int o = 0; o < outer_b; ++o) {
-          bulk_load(sfb_s + o * C::kSfaBytes, sfb_g + o * sfb_outer_stride, sf_bytes, bar);
-        }
-        sfa_g += C::kSfChunks * 512;
-        sfb_g += C::kSfChunks * 512;
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -233,9 +336,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
    if (lane == 0) {
     // ------------------------------ MMA issuer ------------------------------
     const uint32_t idesc = make_idesc<kFmt, kBN>();
-    const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
     int stage = 0;
     uint32_t phase = 0;
+    uint32_t k = 0;          // stages issued so far; selects the scale-factor buffer
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -244,71 +347,76 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
         tc_fence_after();
       }
       const uint32_t acc = tmem_base + (uint32_t)((it & 1) * C::kAccStride);
-      const int n_idx = tile % g.n_tiles;
-      int outer_b = g.q_outer - n_idx * C::kOuterB;
-      outer_b = outer_b > C::kOuterB ? C::kOuterB : outer_b;
-      for (int ks = 0; ks < g.k_stages; ++ks) {
-        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 3)) { ok = false; break; }
+      for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
+        // scale factors in tensor memory imply the stage's data landed (the scale warps waited for it)
+        if (!mbar_wait(bar_sf_ready + 8 * (k & 1u), (k >> 1) & 1u, abort_flag, g.status, 3)) { ok = false; break; }
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 7)) { ok = false; break; }
         tc_fence_after();
-        int nchunk = g.ntx - ks * C::kSfChunks;
-        nchunk = nchunk > C::kSfChunks ? C::kSfChunks : nchunk;
         const uint32_t a_lo = ((smem_base + stage * C::kStageBytes) & 0x3FFFFu) >> 4;
         const uint32_t b_lo = a_lo + (C::kABytes >> 4);
-        const uint32_t sfa_lo = b_lo + (C::kBBytes >> 4);
-        const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+        const uint32_t sfa_t = tmem_base + C::kSfBuf0 + (k & 1u) * C::kSfBufStride;
+        const uint32_t sfb_t = sfa_t + C::kSfbOff;
         const uint32_t first = ks > 0 ? 1u : 0u;
-        int nmma;
-        if (kFmt == kNvfp4) {
-          nmma = nchunk;  // one MMA (64 elements of K) per scale tile
-        } else {
-          const int rem = g.k - ks * 128;
-          nmma = rem >= 128 ? 4 : (rem + 31) / 32;
-        }
-        if (nchunk == C::kSfChunks && outer_b == C::kOuterB && nmma == 4) {
-          // full stage: straight-line issue, every address is base + constant
+        // K beyond the matrix is zero codes times zero scales, so every stage issues all four MMAs.
 #pragma unroll
-          for (int c = 0; c < C::kSfChunks; ++c) {
-            tc_cp_sf(sfa_t + c * 4, make_desc(sfa_lo + c * 32, kDescHiSf));
-#pragma unroll
-            for (int o = 0; o < C::kOuterB; ++o) {
-              tc_cp_sf(sfb_t + c * (kBN / 32) + o * 4, make_desc(sfb_lo + (o * C::kSfChunks + c) * 32, kDescHiSf));
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (kFmt == kNvfp4) {
-              tc_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand), idesc,
-                           j == 0 ? first : 1u, sfa_t + j * 4, sfb_t + j * (kBN / 32));
-            } else {
-              tc_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand),
-                           idesc | ((uint32_t)j << 29) | ((uint32_t)j << 4), j == 0 ? first : 1u, sfa_t, sfb_t);
-            }
-          }
-        } else {
-          for (int c = 0; c < nchunk; ++c) {
-            tc_cp_sf(sfa_t + c * 4, make_desc(sfa_lo + c * 32, kDescHiSf));
-            for (int o = 0; o < outer_b; ++o) {
-              tc_cp_sf(sfb_t + c * (kBN / 32) + o * 4, make_desc(sfb_lo + (o * C::kSfChunks + c) * 32, kDescHiSf));
-            }
-          }
-          for (int j = 0; j < nmma; ++j) {
-            const uint32_t accumulate = (ks > 0 || j > 0) ? 1u : 0u;
-            if (kFmt == kNvfp4) {
-              tc_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand), idesc,
-                           accumulate, sfa_t + j * 4, sfb_t + j * (kBN / 32));
-            } else {
-              tc_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand),
-                           idesc | ((uint32_t)j << 29) | ((uint32_t)j << 4), accumulate, sfa_t, sfb_t);
-            }
+        for (int j = 0; j < 4; ++j) {
+          if (kFmt == kNvfp4) {
+            tc_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand), idesc,
+                         j == 0 ? first : 1u, sfa_t + j * 4, sfb_t + j * (kBN / 32));
+          } else {
+            tc_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand),
+                         idesc | ((uint32_t)j << 29) | ((uint32_t)j << 4), j == 0 ? first : 1u, sfa_t, sfb_t);
           }
         }
-        tc_commit(bar_empty + 8 * stage);
+        tc_commit(bar_empty + 8 * stage);   // frees the stage and its scale-factor buffer
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
       if (ok) tc_commit(bar_tmem_full);
     }
    }
    __syncwarp();
+  } else if (warp >= 8) {
+    // ------------------------------ scale-factor warps ------------------------------
+    // Each warp owns one 32-lane quadrant of tensor memory and writes the same scale image into
+    // it: lane l of a 512-byte scale tile is its 16 bytes at offset 16*l, i.e. four columns.
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t k = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
+        const uint32_t stage = k % C::kStages, use = k / C::kStages;
+        // every lane polls (no broadcast hop); the scale bytes are in registers before the wait
+        // for the tensor-memory buffer, so only store + signal sit between MMA(k-2) and MMA(k)
+        if (!mbar_wait(bar_full + 8 * stage, use & 1u, abort_flag, g.status, 5)) { ok = false; break; }
+        const uint8_t* sfa_s = smem_gen + stage * C::kStageBytes + C::kABytes + C::kBBytes;
+        const uint8_t* sfb_s = sfa_s + C::kSfaBytes;
+        uint32_t va[C::kSfChunks * 4], vb[C::kSfChunks * C::kOuterB * 4];
+#pragma unroll
+        for (int c = 0; c < C::kSfChunks; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(sfa_s + c * 512 + lane * 16);
+          va[4 * c] = v.x; va[4 * c + 1] = v.y; va[4 * c + 2] = v.z; va[4 * c + 3] = v.w;
+#pragma unroll
+          for (int o = 0; o < C::kOuterB; ++o) {
+            const uint4 u = *reinterpret_cast<const uint4*>(sfb_s + (o * C::kSfChunks + c) * 512 + lane * 16);
+            const int j = (c * C::kOuterB + o) * 4;   // column order in tensor memory: chunk-major, then outer tile
+            vb[j] = u.x; vb[j + 1] = u.y; vb[j + 2] = u.z; vb[j + 3] = u.w;
+          }
+        }
+        if (k >= 2) {   // the MMAs that read this scale-factor buffer two stages ago are done
+          const uint32_t j = k - 2;
+          if (!mbar_wait(bar_empty + 8 * (j % C::kStages), (j / C::kStages) & 1u, abort_flag, g.status, 6)) { ok = false; break; }
+        }
+        tc_fence_after();
+        const uint32_t sfa_t = tmem_base + lane_sel + C::kSfBuf0 + (k & 1u) * C::kSfBufStride;
+        const uint32_t sfb_t = sfa_t + C::kSfbOff;
+        tc_st_n<C::kSfChunks * 4>(sfa_t, va);
+        tc_st_n<C::kSfChunks * C::kOuterB * 4>(sfb_t, vb);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sf_ready + 8 * (k & 1u));
+      }
+    }
   } else if (warp >= 4) {
     // ------------------------------ epilogue ------------------------------
     const int quad = warp & 3;
@@ -323,74 +431,40 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((it & 1) * C::kAccStride);
       const int row = m_idx * kBM + quad * 32 + lane;
       const bool row_ok = row < g.rows;
-      // Drain order: the columns the other accumulator overlaps come first.
-      const bool tail_first = (kBN == 256) && ((it & 1) == 0);
-#pragma unroll 1
-      for (int ci = 0; ci < C::kChunks; ++ci) {
-        int c = ci;
-        if (tail_first) c = ci < C::kEarlyChunks ? C::kChunks - 1 - ci : ci - C::kEarlyChunks;
-        uint32_t r[32];
-        tc_ld32(acc + (uint32_t)(c * 32), r);
+      const int col_base = n_idx * kBN;
+      if (kBN == 256) {
+        // The columns the other accumulator overlaps (the last 96 of accumulator 0, the first 96
+        // of accumulator 1) go to registers first; then the MMA warp may start the next tile.
+        const int e0 = (it & 1) == 0 ? C::kChunks - C::kEarlyChunks : 0;
+        uint32_t early[3][32];
+#pragma unroll
+        for (int e = 0; e < 3; ++e) tc_ld32(acc + (uint32_t)((e0 + e) * 32), early[e]);
         tc_wait_ld();
-        if (ci == C::kEarlyChunks - 1) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_tmem_empty);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tmem_empty);
+#pragma unroll
+        for (int e = 0; e < 3; ++e) store_chunk(g, row, row_ok, col_base + (e0 + e) * 32, early[e]);
+        const int r0 = (it & 1) == 0 ? 0 : C::kEarlyChunks;
+#pragma unroll 1
+        for (int ci = 0; ci < C::kChunks - C::kEarlyChunks; ++ci) {
+          uint32_t r[32];
+          tc_ld32(acc + (uint32_t)((r0 + ci) * 32), r);
+          tc_wait_ld();
+          store_chunk(g, row, row_ok, col_base + (r0 + ci) * 32, r);
         }
-        const int col0 = n_idx * kBN + c * 32;
-        if (row_ok && col0 < g.cols) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (g.bias != nullptr) {
-            if (g.vec_ok && col0 + 32 <= g.cols) {
-              const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                const uint4 b = __ldg(bp + q4);
-                const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  v[q4 * 8 + 2 * j] += __uint_as_float(bw[j] << 16);
-                  v[q4 * 8 + 2 * j + 1] += __uint_as_float(bw[j] & 0xFFFF0000u);
-                }
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < g.cols) v[j] += __bfloat162float(g.bias[col0 + j]);
-            }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < C::kChunks; ++c) {
+          uint32_t r[32];
+          tc_ld32(acc + (uint32_t)(c * 32), r);
+          tc_wait_ld();
+          if (c == C::kChunks - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tmem_empty);
           }
-          if (g.out_f32) {
-            float* dp = static_cast<float*>(g.d) + (int64_t)row * g.ldd + col0;
-            if (g.vec_ok && col0 + 32 <= g.cols) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<float4*>(dp)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < g.cols) dp[j] = v[j];
-            }
-          } else {
-            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(g.d) + (int64_t)row * g.ldd + col0;
-            if (g.vec_ok && col0 + 32 <= g.cols) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint32_t w[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
-                  w[t] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                reinterpret_cast<uint4*>(dp)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < g.cols) dp[j] = __float2bfloat16_rn(v[j]);
-            }
-          }
+          store_chunk(g, row, row_ok, col_base + c * 32, r);
         }
       }
     }
@@ -407,6 +481,280 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 }
 
 // ------------------------------------------------------------------------------------
+// Two-CTA variant: a cluster of two CTAs (two SMs) works on one 256 x kBN tile with
+// cta_group::2 MMAs.  Each CTA holds its own 128 rows of P and HALF of the Q rows in shared
+// memory (the MMA reads both halves across the pair), so the Q-operand traffic per SM is
+// halved compared with the one-CTA kernel; the accumulator of each CTA is 128 lanes x kBN
+// columns in its own tensor memory.  Every load is a plain tiled TMA load (no multicast);
+// both CTAs' loads signal the leader CTA's "full" barrier, the leader issues the scale copies
+// and MMAs for the pair and commits to the barriers of both CTAs.
+// ------------------------------------------------------------------------------------
+constexpr int kGemm2Threads = 256;
+
+template <int kFmt, int kBN>
+struct Cfg2 {
+  static constexpr int kSfChunks = kFmt == kNvfp4 ? 4 : 1;
+  static constexpr int kOuterB = kBN / 128;
+  static constexpr int kABytes = kBM * 128;
+  static constexpr int kBBytes = (kBN / 2) * 128;            // this CTA's half of the Q slab
+  static constexpr int kSfaBytes = kSfChunks * 512;
+  static constexpr int kSfbBytes = kOuterB * kSfChunks * 512;  // scales of ALL kBN columns
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kStages = (220 * 1024) / kStageBytes > 8 ? 8 : (220 * 1024) / kStageBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+  // tensor memory: accumulators at 0 and kAccStride, scale factors in columns 464..511
+  static constexpr int kAccStride = (kBN == 256) ? 208 : 128;
+  static constexpr int kChunks = kBN / 32;
+  static constexpr int kEarlyChunks = (kBN == 256) ? 2 : kChunks;
+  static constexpr int kSfaCol = kSfTmemBase;
+  static constexpr int kSfbCol = kSfTmemBase + 16;
+  static constexpr int kSfBoxElems = kSfChunks * 64;         // 8-byte elements per scale box row
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+  static_assert(kAccStride + kBN <= kSfTmemBase, "tensor memory budget");
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive (+ expected bytes) on an mbarrier that may live in the other CTA of the cluster
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tiled TMA load of a CTA pair member: data into this CTA, completion bytes to `bar` (cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc2_commit(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tc2_cp_sf(uint32_t tmem_addr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+template <int kFmt>
+__device__ __forceinline__ void tc2_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate, uint32_t sfa, uint32_t sfb) {
+  if (kFmt == kNvfp4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+
+template <int kFmt, int kBN>
+__global__ void __launch_bounds__(kGemm2Threads, 1)
+gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                         const __grid_constant__ CUtensorMap map_psf, const __grid_constant__ CUtensorMap map_qsf,
+                         const GemmParams g) {
+  using C = Cfg2<kFmt, kBN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kStages * C::kStageBytes);
+  const uint32_t bar_full = smem_u32(bars);                    // [kStages] data of both CTAs landed (leader's copy is used)
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;        // [kStages] MMAs that read the stage are done
+  const uint32_t bar_tmem_full = bar_empty + 8 * C::kStages;   // [1]
+  const uint32_t bar_tmem_empty = bar_tmem_full + 8;           // [1] (leader's copy is used)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0 = leader
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);      // the leader's producer arms it with the bytes of BOTH CTAs
+      mbar_init(bar_empty + 8 * s, 1);     // one tcgen05.commit
+    }
+    mbar_init(bar_tmem_full, 1);
+    mbar_init(bar_tmem_empty, 8);          // four epilogue warps in each CTA
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // barriers of both CTAs are initialised before any remote arrive
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // pair tile = 256 rows x kBN columns
+  const int pair_m_tiles = (g.m_tiles + 1) >> 1;
+  const int num_tiles = pair_m_tiles * g.n_tiles;
+  const uint32_t leader_full = mapa_u32(bar_full, 0);
+  const uint32_t leader_tmem_empty = mapa_u32(bar_tmem_empty, 0);
+
+  if (warp == 0) {
+   if (lane == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
+      const int m_tile = pm * 2 + (int)rank;                 // this CTA's 128-row tile of P
+      const int row_p = m_tile * kBM;
+      const int row_q = n_idx * kBN + (int)rank * (kBN / 2);  // this CTA's half of the Q rows
+      for (int ks = 0; ks < g.k_stages; ++ks) {
+        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 21)) { ok = false; break; }
+        const uint32_t a_s = smem_base + stage * C::kStageBytes;
+        const uint32_t b_s = a_s + C::kABytes;
+        const uint32_t sfa_s = b_s + C::kBBytes;
+        const uint32_t sfb_s = sfa_s + C::kSfaBytes;
+        const uint32_t bar = leader_full + 8 * stage;
+        // Only the leader arms the barrier, with the bytes both CTAs are about to load; the
+        // other CTA's copies simply complete on it (its arrival count keeps the phase open).
+        if (leader) mbar_expect_tx(bar_full + 8 * stage, 2u * (uint32_t)C::kStageBytes);
+        tma_load_2d_pair(a_s, &map_p, bar, ks * 128, row_p);
+        tma_load_2d_pair(b_s, &map_q, bar, ks * 128, row_q);
+        tma_load_2d_pair(sfa_s, &map_psf, bar, ks * C::kSfBoxElems, m_tile);
+#pragma unroll
+        for (int o = 0; o < C::kOuterB; ++o) {
+          tma_load_2d_pair(sfb_s + o * C::kSfaBytes, &map_qsf, bar, ks * C::kSfBoxElems, n_idx * C::kOuterB + o);
+        }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (*abort_flag) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {}
+    }
+   }
+   __syncwarp();
+  } else if (warp == 1) {
+   if (lane == 0 && leader) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    const uint32_t idesc = (make_idesc<kFmt, kBN>() & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24);  // M = 256
+    const uint32_t peer_empty = mapa_u32(bar_empty, 1), peer_tmem_full = mapa_u32(bar_tmem_full, 1);
+    int stage = 0;
+    uint32_t phase = 0;
+    const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+    int it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+      if (it > 0) {
+        if (!mbar_wait(bar_tmem_empty, (uint32_t)((it - 1) & 1), abort_flag, g.status, 22)) { ok = false; break; }
+        tc_fence_after();
+      }
+      const uint32_t acc = tmem_base + (uint32_t)((it & 1) * C::kAccStride);
+      for (int ks = 0; ks < g.k_stages; ++ks) {
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 23)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_lo = ((smem_base + stage * C::kStageBytes) & 0x3FFFFu) >> 4;
+        const uint32_t b_lo = a_lo + (C::kABytes >> 4);
+        const uint32_t sfa_lo = b_lo + (C::kBBytes >> 4);
+        const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+        const uint32_t first = ks > 0 ? 1u : 0u;
+        // Out-of-range K reads as zero codes and zero scales, so every stage issues all four MMAs.
+#pragma unroll
+        for (int c = 0; c < C::kSfChunks; ++c) {
+          tc2_cp_sf(sfa_t + c * 4, make_desc(sfa_lo + c * 32, kDescHiSf));
+#pragma unroll
+          for (int o = 0; o < C::kOuterB; ++o) {
+            tc2_cp_sf(sfb_t + c * (kBN / 32) + o * 4, make_desc(sfb_lo + (o * C::kSfChunks + c) * 32, kDescHiSf));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (kFmt == kNvfp4) {
+            tc2_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand), idesc,
+                          j == 0 ? first : 1u, sfa_t + j * 4, sfb_t + j * (kBN / 32));
+          } else {
+            tc2_mma<kFmt>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand),
+                          idesc | ((uint32_t)j << 29) | ((uint32_t)j << 4), j == 0 ? first : 1u, sfa_t, sfb_t);
+          }
+        }
+        tc2_commit(bar_empty + 8 * stage);     // frees the stage (and its scale-factor buffer) in this CTA ...
+        tc2_commit(peer_empty + 8 * stage);    // ... and in the other one
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) {
+        tc2_commit(bar_tmem_full);
+        tc2_commit(peer_tmem_full);
+      }
+    }
+   }
+   __syncwarp();
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int quad = warp & 3;
+    int it = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
+      const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(bar_tmem_full, (uint32_t)(it & 1), abort_flag, g.status, 24) ? 1 : 0;
+      ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((it & 1) * C::kAccStride);
+      const int row = (pm * 2 + (int)rank) * kBM + quad * 32 + lane;
+      const bool row_ok = row < g.rows;
+      const bool tail_first = (kBN == 256) && ((it & 1) == 0);
+#pragma unroll 1
+      for (int ci = 0; ci < C::kChunks; ++ci) {
+        int c = ci;
+        if (tail_first) c = ci < C::kEarlyChunks ? C::kChunks - 1 - ci : ci - C::kEarlyChunks;
+        uint32_t r[32];
+        tc_ld32(acc + (uint32_t)(c * 32), r);
+        tc_wait_ld();
+        if (ci == C::kEarlyChunks - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);
+        }
+        store_chunk(g, row, row_ok, n_idx * kBN + c * 32, r);
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // the other CTA no longer signals into this one's shared memory
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------
 // K-major byte matrix [outer, kbytes] -> tensor map with a {128 bytes, box_rows} box, 128-byte swizzle.
@@ -415,23 +763,103 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t outer, int64_t 
                               (uint64_t)kbytes, 128u, (uint32_t)box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+// Scale buffer (128x4 tile layout) as a 2-D matrix of 8-byte words: one row per 128-row band,
+// 64 words per 512-byte tile.  A box of `box_words` words is the scale data of one K stage.
+int make_sf_map(CUtensorMap* map, const void* base, int64_t outer, int64_t ntx, int box_words) {
+  return encode_tensor_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, base, (uint64_t)ntx * 64,
+                              (uint64_t)ceil_div(outer, 128), (uint64_t)ntx * 512, (uint32_t)box_words, 1u,
+                              CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 template <int kFmt, int kBN>
 int launch_gemm(const void* p_codes, const void* q_codes, const GemmParams& g0, int64_t kbytes, cudaStream_t stream) {
   using C = Cfg<kFmt, kBN>;
   GemmParams g = g0;
   g.n_tiles = (int)ceil_div(g.cols, kBN);
-  CUtensorMap map_p, map_q;
+  CUtensorMap map_p, map_q, map_psf, map_qsf;
   int rc = make_operand_map(&map_p, p_codes, g.rows, kbytes, kBM);
   if (rc != FP4T_OK) return rc;
   rc = make_operand_map(&map_q, q_codes, g.cols, kbytes, kBN);
+  if (rc != FP4T_OK) return rc;
+  rc = make_sf_map(&map_psf, g.p_sf, g.rows, g.ntx, C::kSfBoxElems);
+  if (rc != FP4T_OK) return rc;
+  rc = make_sf_map(&map_qsf, g.q_sf, g.cols, g.ntx, C::kSfBoxElems);
   if (rc != FP4T_OK) return rc;
   auto kern = gemm_blockscaled_kernel<kFmt, kBN>;
   FP4T_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   const int sms = sm_count();
   const int tiles = g.m_tiles * g.n_tiles;
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(map_p, map_q, g);
+  kern<<<grid, kGemm1Threads, C::kSmemBytes, stream>>>(map_p, map_q, map_psf, map_qsf, g);
   FP4T_CUDA(cudaGetLastError());
+  return FP4T_OK;
+}
+
+template <int kFmt, int kBN>
+int max_clusters() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    using C = Cfg2<kFmt, kBN>;
+    auto kern = gemm2_blockscaled_kernel<kFmt, kBN>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
+      cached[dev] = -1;
+      return -1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 148, 1, 1);
+    cfg.blockDim = dim3(kGemm2Threads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = -1;
+    }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+template <int kFmt, int kBN>
+int launch_gemm2(const void* p_codes, const void* q_codes, const GemmParams& g0, int64_t kbytes, int clusters,
+                 cudaStream_t stream) {
+  using C = Cfg2<kFmt, kBN>;
+  GemmParams g = g0;
+  g.n_tiles = (int)ceil_div(g.cols, kBN);
+  CUtensorMap map_p, map_q, map_psf, map_qsf;
+  int rc = make_operand_map(&map_p, p_codes, g.rows, kbytes, kBM);
+  if (rc != FP4T_OK) return rc;
+  rc = make_operand_map(&map_q, q_codes, g.cols, kbytes, kBN / 2);
+  if (rc != FP4T_OK) return rc;
+  rc = make_sf_map(&map_psf, g.p_sf, g.rows, g.ntx, C::kSfBoxElems);
+  if (rc != FP4T_OK) return rc;
+  rc = make_sf_map(&map_qsf, g.q_sf, g.cols, g.ntx, C::kSfBoxElems);
+  if (rc != FP4T_OK) return rc;
+  const int pair_tiles = ((g.m_tiles + 1) / 2) * g.n_tiles;
+  const int nclusters = pair_tiles < clusters ? pair_tiles : clusters;
+  if (getenv("FP4T_VERBOSE")) fprintf(stderr, "[fp4t] gemm2 fmt=%d BN=%d clusters=%d (max %d) pair_tiles=%d stages=%d\n", kFmt, kBN, nclusters, clusters, pair_tiles, C::kStages);
+  auto kern = gemm2_blockscaled_kernel<kFmt, kBN>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * nclusters, 1, 1);
+  cfg.blockDim = dim3(kGemm2Threads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FP4T_CUDA(cudaLaunchKernelEx(&cfg, kern, map_p, map_q, map_psf, map_qsf, g));
   return FP4T_OK;
 }
 
@@ -479,6 +907,19 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
   g.status = status;
   g.n_tiles = 0;
 
+  // Two-CTA kernel whenever there are at least two 128-row tiles (FP4T_GEMM_1CTA=1 keeps the
+  // one-CTA kernel, for comparisons).
+  static const bool force_1cta = [] { const char* e = getenv("FP4T_GEMM_1CTA"); return e && e[0] == '1'; }();
+  if (g.m_tiles >= 2 && !force_1cta) {
+    const int c256 = max_clusters<kFmt, 256>(), c128 = max_clusters<kFmt, 128>();
+    if (c256 > 0 && c128 > 0) {
+      const int64_t pm = (g.m_tiles + 1) / 2;
+      const double k256 = (double)ceil_div(pm * ceil_div(cols, 256), c256) * 256.0;
+      const double k128 = (double)ceil_div(pm * ceil_div(cols, 128), c128) * 128.0 * 1.10;
+      if (k256 <= k128) return launch_gemm2<kFmt, 256>(p_codes, q_codes, g, kbytes, c256, stream);
+      return launch_gemm2<kFmt, 128>(p_codes, q_codes, g, kbytes, c128, stream);
+    }
+  }
   // Tile width: fewer, wider tiles unless narrow ones fill the machine better.
   const int64_t t256 = (int64_t)g.m_tiles * ceil_div(cols, 256), t128 = (int64_t)g.m_tiles * ceil_div(cols, 128);
   const double cost256 = (double)ceil_div(t256, sms) * 256.0;

@@ -55,7 +55,7 @@ MX_ZERO_BLOCK_AMAX = 2.0 ** -126  # all-zero block: exponent of the smallest fp3
 
 def e2m1_decode(codes: torch.Tensor) -> torch.Tensor:
     """4-bit codes (uint8, 0..15) -> fp32 values; bit 3 is the sign."""
-    grid = torch.tensor(E2M1_GRID, dtype=torch.float32)
+    grid = torch.tensor(E2M1_GRID, dtype=torch.float32, device=codes.device)
     mag = grid[(codes & 7).long()]
     return torch.where((codes & 8) != 0, -mag, mag)
 
@@ -86,7 +86,7 @@ def pack_fp4_pairs(codes: torch.Tensor) -> torch.Tensor:
 
 
 def unpack_fp4_pairs(packed: torch.Tensor) -> torch.Tensor:
-    out = torch.empty(packed.shape[0], packed.shape[1] * 2, dtype=torch.uint8)
+    out = torch.empty(packed.shape[0], packed.shape[1] * 2, dtype=torch.uint8, device=packed.device)
     out[:, 0::2] = packed & 0xF
     out[:, 1::2] = packed >> 4
     return out
@@ -353,6 +353,46 @@ def nvfp4_linear_fwd_bwd(x, w, g, b=None, noise_g=None, noise_gt=None):
     dw = gemm_dequant_fp32(deq(g.t().contiguous(), noise_gt), deq(x.t().contiguous()))
     db = g.float().sum(dim=0) if b is not None else None
     return y, dx, dw, db
+
+
+class OracleNvfp4Linear(torch.autograd.Function):
+    """The reference recipe of custom/linear/nvfp4.py:25-90 as plain torch arithmetic on
+    dequantized operands, on whatever device the tensors live: every operand goes through the
+    restated quantizer, stochastic rounding (dgrad operand first, then wgrad operand, as the
+    reference draws them) uses torch.rand on that device, GEMMs are fp32 matmuls whose result
+    is rounded to the input dtype.  Used by tests to check that training with the CUDA
+    kernels follows the same loss curve."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        dt = x.dtype
+        xq = x.to(torch.bfloat16) if dt != torch.float32 else x
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = b is not None
+
+        def deq(t, noise=None):
+            c, s = nvfp4_quantize_rowwise(t, noise)
+            return nvfp4_dequant(c, s)
+        y = deq(xq) @ deq(w.to(xq.dtype)).t()
+        if b is not None:
+            y = y + b.to(torch.bfloat16).float()
+        return y.to(dt)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        g = g.contiguous()
+
+        def deq(t, noise=None):
+            c, s = nvfp4_quantize_rowwise(t, noise)
+            return nvfp4_dequant(c, s)
+        n, oc = g.shape
+        u = torch.rand(n, oc // 16, 16, device=g.device)
+        ut = torch.rand(oc, n // 16, 16, device=g.device)
+        dx = deq(g, u) @ deq(w.to(g.dtype).t().contiguous()).t()
+        dw = deq(g.t().contiguous(), ut) @ deq(x.to(g.dtype).t().contiguous()).t()
+        db = g.sum(dim=0) if ctx.has_bias else None
+        return dx.to(g.dtype), dw.to(g.dtype), db
 
 
 # ----------------------------------------------------------------------------
