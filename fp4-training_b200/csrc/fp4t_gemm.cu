@@ -66,8 +66,9 @@ struct Cfg {
   static constexpr int kChunks = kBN / 32;                     // 32-column epilogue chunks
   static constexpr int kEarlyChunks = (kBN == 256) ? 3 : 0;    // chunks the other accumulator overlaps
   static constexpr int kSfBuf0 = 416;
-  static constexpr int kSfBufStride = 48;
-  static constexpr int kSfbOff = 16;                           // SFB columns follow the 16 SFA columns
+  static constexpr int kSfbOff = kSfChunks * 4;                // SFB columns follow the SFA columns
+  static constexpr int kSfBufStride = kSfChunks * 4 + kSfChunks * kOuterB * 4;   // columns of one stage's scales
+  static constexpr int kSfBufs = (96 / kSfBufStride) > 4 ? 4 : (96 / kSfBufStride);  // ring depth (2 for NVFP4)
   static constexpr int kSfBoxElems = kSfChunks * 64;           // 8-byte words per scale box row
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   static_assert(kAccStride + kBN <= kSfBuf0, "tensor memory budget");
@@ -264,9 +265,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
   const uint32_t bar_full = smem_u32(bars);                       // [kStages] stage data landed
   const uint32_t bar_empty = bar_full + 8 * C::kStages;           // [kStages] MMAs that read the stage are done
   const uint32_t bar_sf_ready = bar_empty + 8 * C::kStages;       // [2] scale factors are in tensor memory
-  const uint32_t bar_tmem_full = bar_sf_ready + 16;               // [1]
+  const uint32_t bar_tmem_full = bar_sf_ready + 32;               // [1]
   const uint32_t bar_tmem_empty = bar_tmem_full + 8;              // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -277,8 +278,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_sf_ready, 4);
-    mbar_init(bar_sf_ready + 8, 4);
+    for (int b = 0; b < C::kSfBufs; ++b) mbar_init(bar_sf_ready + 8 * b, 4);
     mbar_init(bar_tmem_full, 1);
     mbar_init(bar_tmem_empty, 4);
     *abort_flag = 0;
@@ -349,12 +349,12 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       const uint32_t acc = tmem_base + (uint32_t)((it & 1) * C::kAccStride);
       for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
         // scale factors in tensor memory imply the stage's data landed (the scale warps waited for it)
-        if (!mbar_wait(bar_sf_ready + 8 * (k & 1u), (k >> 1) & 1u, abort_flag, g.status, 3)) { ok = false; break; }
+        if (!mbar_wait(bar_sf_ready + 8 * (k % C::kSfBufs), (k / C::kSfBufs) & 1u, abort_flag, g.status, 3)) { ok = false; break; }
         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 7)) { ok = false; break; }
         tc_fence_after();
         const uint32_t a_lo = ((smem_base + stage * C::kStageBytes) & 0x3FFFFu) >> 4;
         const uint32_t b_lo = a_lo + (C::kABytes >> 4);
-        const uint32_t sfa_t = tmem_base + C::kSfBuf0 + (k & 1u) * C::kSfBufStride;
+        const uint32_t sfa_t = tmem_base + C::kSfBuf0 + (k % C::kSfBufs) * C::kSfBufStride;
         const uint32_t sfb_t = sfa_t + C::kSfbOff;
         const uint32_t first = ks > 0 ? 1u : 0u;
         // K beyond the matrix is zero codes times zero scales, so every stage issues all four MMAs.
@@ -402,19 +402,19 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
             vb[j] = u.x; vb[j + 1] = u.y; vb[j + 2] = u.z; vb[j + 3] = u.w;
           }
         }
-        if (k >= 2) {   // the MMAs that read this scale-factor buffer two stages ago are done
-          const uint32_t j = k - 2;
+        if (k >= (uint32_t)C::kSfBufs) {   // the MMAs that last read this scale-factor buffer are done
+          const uint32_t j = k - C::kSfBufs;
           if (!mbar_wait(bar_empty + 8 * (j % C::kStages), (j / C::kStages) & 1u, abort_flag, g.status, 6)) { ok = false; break; }
         }
         tc_fence_after();
-        const uint32_t sfa_t = tmem_base + lane_sel + C::kSfBuf0 + (k & 1u) * C::kSfBufStride;
+        const uint32_t sfa_t = tmem_base + lane_sel + C::kSfBuf0 + (k % C::kSfBufs) * C::kSfBufStride;
         const uint32_t sfb_t = sfa_t + C::kSfbOff;
         tc_st_n<C::kSfChunks * 4>(sfa_t, va);
         tc_st_n<C::kSfChunks * C::kOuterB * 4>(sfb_t, vb);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_sf_ready + 8 * (k & 1u));
+        if (lane == 0) mbar_arrive(bar_sf_ready + 8 * (k % C::kSfBufs));
       }
     }
   } else if (warp >= 4) {
@@ -489,7 +489,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 // both CTAs' loads signal the leader CTA's "full" barrier, the leader issues the scale copies
 // and MMAs for the pair and commits to the barriers of both CTAs.
 // ------------------------------------------------------------------------------------
-constexpr int kGemm2Threads = 256;
+constexpr int kGemm2Threads = 384;
 
 template <int kFmt, int kBN>
 struct Cfg2 {
@@ -502,15 +502,17 @@ struct Cfg2 {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kStages = (220 * 1024) / kStageBytes > 8 ? 8 : (220 * 1024) / kStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
-  // tensor memory: accumulators at 0 and kAccStride, scale factors in columns 464..511
-  static constexpr int kAccStride = (kBN == 256) ? 208 : 128;
+  // tensor memory: accumulators at 0 and kAccStride, two 48-column scale-factor buffers at 416 and 464
+  static constexpr int kAccStride = (kBN == 256) ? 160 : 128;
   static constexpr int kChunks = kBN / 32;
-  static constexpr int kEarlyChunks = (kBN == 256) ? 2 : kChunks;
-  static constexpr int kSfaCol = kSfTmemBase;
-  static constexpr int kSfbCol = kSfTmemBase + 16;
+  static constexpr int kEarlyChunks = (kBN == 256) ? 3 : 0;
+  static constexpr int kSfBuf0 = 416;
+  static constexpr int kSfbOff = kSfChunks * 4;
+  static constexpr int kSfBufStride = kSfChunks * 4 + kSfChunks * kOuterB * 4;
+  static constexpr int kSfBufs = (96 / kSfBufStride) > 4 ? 4 : (96 / kSfBufStride);
   static constexpr int kSfBoxElems = kSfChunks * 64;         // 8-byte elements per scale box row
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-  static_assert(kAccStride + kBN <= kSfTmemBase, "tensor memory budget");
+  static_assert(kAccStride + kBN <= kSfBuf0, "tensor memory budget");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -532,8 +534,10 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, ui
                "r"(bytes)
                : "memory");
 }
+// Arrive on an mbarrier of either CTA of the pair.  What is handed over lives in tensor memory
+// (ordered by the tcgen05 fences), so no cluster-scope release of ordinary memory is requested.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // tiled TMA load of a CTA pair member: data into this CTA, completion bytes to `bar` (cluster address)
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
@@ -580,9 +584,11 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kStages * C::kStageBytes);
   const uint32_t bar_full = smem_u32(bars);                    // [kStages] data of both CTAs landed (leader's copy is used)
   const uint32_t bar_empty = bar_full + 8 * C::kStages;        // [kStages] MMAs that read the stage are done
-  const uint32_t bar_tmem_full = bar_empty + 8 * C::kStages;   // [1]
+  const uint32_t bar_sf_land = bar_empty + 8 * C::kStages;     // [kStages] this CTA's own scale tiles landed
+  const uint32_t bar_sf_ready = bar_sf_land + 8 * C::kStages;  // [2] scale factors are in tensor memory (leader's copy)
+  const uint32_t bar_tmem_full = bar_sf_ready + 32;            // [1]
   const uint32_t bar_tmem_empty = bar_tmem_full + 8;           // [1] (leader's copy is used)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * C::kStages + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -596,7 +602,9 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);      // the leader's producer arms it with the bytes of BOTH CTAs
       mbar_init(bar_empty + 8 * s, 1);     // one tcgen05.commit
+      mbar_init(bar_sf_land + 8 * s, 1);
     }
+    for (int b = 0; b < C::kSfBufs; ++b) mbar_init(bar_sf_ready + 8 * b, 8);   // four scale warps in each CTA
     mbar_init(bar_tmem_full, 1);
     mbar_init(bar_tmem_empty, 8);          // four epilogue warps in each CTA
     *abort_flag = 0;
@@ -619,6 +627,7 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   const int num_tiles = pair_m_tiles * g.n_tiles;
   const uint32_t leader_full = mapa_u32(bar_full, 0);
   const uint32_t leader_tmem_empty = mapa_u32(bar_tmem_empty, 0);
+  const uint32_t leader_sf_ready = mapa_u32(bar_sf_ready, 0);
 
   if (warp == 0) {
    if (lane == 0) {
@@ -640,14 +649,16 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
         const uint32_t bar = leader_full + 8 * stage;
         // Only the leader arms the barrier, with the bytes both CTAs are about to load; the
         // other CTA's copies simply complete on it (its arrival count keeps the phase open).
-        if (leader) mbar_expect_tx(bar_full + 8 * stage, 2u * (uint32_t)C::kStageBytes);
-        tma_load_2d_pair(a_s, &map_p, bar, ks * 128, row_p);
-        tma_load_2d_pair(b_s, &map_q, bar, ks * 128, row_q);
-        tma_load_2d_pair(sfa_s, &map_psf, bar, ks * C::kSfBoxElems, m_tile);
+        const uint32_t sbar = bar_sf_land + 8 * stage;
+        mbar_expect_tx(sbar, (uint32_t)(C::kSfaBytes + C::kSfbBytes));
+        tma_load_2d(sfa_s, &map_psf, sbar, ks * C::kSfBoxElems, m_tile);
 #pragma unroll
         for (int o = 0; o < C::kOuterB; ++o) {
-          tma_load_2d_pair(sfb_s + o * C::kSfaBytes, &map_qsf, bar, ks * C::kSfBoxElems, n_idx * C::kOuterB + o);
+          tma_load_2d(sfb_s + o * C::kSfaBytes, &map_qsf, sbar, ks * C::kSfBoxElems, n_idx * C::kOuterB + o);
         }
+        if (leader) mbar_expect_tx(bar_full + 8 * stage, 2u * (uint32_t)(C::kABytes + C::kBBytes));
+        tma_load_2d_pair(a_s, &map_p, bar, ks * 128, row_p);
+        tma_load_2d_pair(b_s, &map_q, bar, ks * 128, row_q);
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -664,7 +675,7 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     const uint32_t peer_empty = mapa_u32(bar_empty, 1), peer_tmem_full = mapa_u32(bar_tmem_full, 1);
     int stage = 0;
     uint32_t phase = 0;
-    const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+    uint32_t k = 0;          // stages issued so far; selects the scale-factor buffer
     int it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
@@ -673,23 +684,16 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
         tc_fence_after();
       }
       const uint32_t acc = tmem_base + (uint32_t)((it & 1) * C::kAccStride);
-      for (int ks = 0; ks < g.k_stages; ++ks) {
+      for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
+        if (!mbar_wait(bar_sf_ready + 8 * (k % C::kSfBufs), (k / C::kSfBufs) & 1u, abort_flag, g.status, 25)) { ok = false; break; }
         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 23)) { ok = false; break; }
         tc_fence_after();
         const uint32_t a_lo = ((smem_base + stage * C::kStageBytes) & 0x3FFFFu) >> 4;
         const uint32_t b_lo = a_lo + (C::kABytes >> 4);
-        const uint32_t sfa_lo = b_lo + (C::kBBytes >> 4);
-        const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+        const uint32_t sfa_t = tmem_base + C::kSfBuf0 + (k % C::kSfBufs) * C::kSfBufStride;
+        const uint32_t sfb_t = sfa_t + C::kSfbOff;
         const uint32_t first = ks > 0 ? 1u : 0u;
-        // Out-of-range K reads as zero codes and zero scales, so every stage issues all four MMAs.
-#pragma unroll
-        for (int c = 0; c < C::kSfChunks; ++c) {
-          tc2_cp_sf(sfa_t + c * 4, make_desc(sfa_lo + c * 32, kDescHiSf));
-#pragma unroll
-          for (int o = 0; o < C::kOuterB; ++o) {
-            tc2_cp_sf(sfb_t + c * (kBN / 32) + o * 4, make_desc(sfb_lo + (o * C::kSfChunks + c) * 32, kDescHiSf));
-          }
-        }
+        // K beyond the matrix is zero codes times zero scales, so every stage issues all four MMAs.
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (kFmt == kNvfp4) {
@@ -711,6 +715,44 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     }
    }
    __syncwarp();
+  } else if (warp >= 8) {
+    // ------------------------------ scale-factor warps (both CTAs) ------------------------------
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t k = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
+        const uint32_t stage = k % C::kStages, use = k / C::kStages;
+        if (!mbar_wait(bar_sf_land + 8 * stage, use & 1u, abort_flag, g.status, 26)) { ok = false; break; }
+        const uint8_t* sfa_s = smem_gen + stage * C::kStageBytes + C::kABytes + C::kBBytes;
+        const uint8_t* sfb_s = sfa_s + C::kSfaBytes;
+        uint32_t va[C::kSfChunks * 4], vb[C::kSfChunks * C::kOuterB * 4];
+#pragma unroll
+        for (int c = 0; c < C::kSfChunks; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(sfa_s + c * 512 + lane * 16);
+          va[4 * c] = v.x; va[4 * c + 1] = v.y; va[4 * c + 2] = v.z; va[4 * c + 3] = v.w;
+#pragma unroll
+          for (int o = 0; o < C::kOuterB; ++o) {
+            const uint4 u = *reinterpret_cast<const uint4*>(sfb_s + (o * C::kSfChunks + c) * 512 + lane * 16);
+            const int j = (c * C::kOuterB + o) * 4;
+            vb[j] = u.x; vb[j + 1] = u.y; vb[j + 2] = u.z; vb[j + 3] = u.w;
+          }
+        }
+        if (k >= (uint32_t)C::kSfBufs) {   // the MMAs that last read this scale-factor buffer are done
+          const uint32_t j = k - C::kSfBufs;
+          if (!mbar_wait(bar_empty + 8 * (j % C::kStages), (j / C::kStages) & 1u, abort_flag, g.status, 27)) { ok = false; break; }
+        }
+        tc_fence_after();
+        const uint32_t sfa_t = tmem_base + lane_sel + C::kSfBuf0 + (k % C::kSfBufs) * C::kSfBufStride;
+        const uint32_t sfb_t = sfa_t + C::kSfbOff;
+        tc_st_n<C::kSfChunks * 4>(sfa_t, va);
+        tc_st_n<C::kSfChunks * C::kOuterB * 4>(sfb_t, vb);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_sf_ready + 8 * (k % C::kSfBufs));
+      }
+    }
   } else if (warp >= 4) {
     // ------------------------------ epilogue (both CTAs) ------------------------------
     const int quad = warp & 3;
@@ -725,20 +767,39 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((it & 1) * C::kAccStride);
       const int row = (pm * 2 + (int)rank) * kBM + quad * 32 + lane;
       const bool row_ok = row < g.rows;
-      const bool tail_first = (kBN == 256) && ((it & 1) == 0);
-#pragma unroll 1
-      for (int ci = 0; ci < C::kChunks; ++ci) {
-        int c = ci;
-        if (tail_first) c = ci < C::kEarlyChunks ? C::kChunks - 1 - ci : ci - C::kEarlyChunks;
-        uint32_t r[32];
-        tc_ld32(acc + (uint32_t)(c * 32), r);
+      const int col_base = n_idx * kBN;
+      if (kBN == 256) {
+        const int e0 = (it & 1) == 0 ? C::kChunks - C::kEarlyChunks : 0;
+        uint32_t early[3][32];
+#pragma unroll
+        for (int e = 0; e < 3; ++e) tc_ld32(acc + (uint32_t)((e0 + e) * 32), early[e]);
         tc_wait_ld();
-        if (ci == C::kEarlyChunks - 1) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);
+#pragma unroll
+        for (int e = 0; e < 3; ++e) store_chunk(g, row, row_ok, col_base + (e0 + e) * 32, early[e]);
+        const int r0 = (it & 1) == 0 ? 0 : C::kEarlyChunks;
+#pragma unroll 1
+        for (int ci = 0; ci < C::kChunks - C::kEarlyChunks; ++ci) {
+          uint32_t r[32];
+          tc_ld32(acc + (uint32_t)((r0 + ci) * 32), r);
+          tc_wait_ld();
+          store_chunk(g, row, row_ok, col_base + (r0 + ci) * 32, r);
         }
-        store_chunk(g, row, row_ok, n_idx * kBN + c * 32, r);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < C::kChunks; ++c) {
+          uint32_t r[32];
+          tc_ld32(acc + (uint32_t)(c * 32), r);
+          tc_wait_ld();
+          if (c == C::kChunks - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);
+          }
+          store_chunk(g, row, row_ok, col_base + c * 32, r);
+        }
       }
     }
   }
@@ -914,16 +975,17 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
     const int c256 = max_clusters<kFmt, 256>(), c128 = max_clusters<kFmt, 128>();
     if (c256 > 0 && c128 > 0) {
       const int64_t pm = (g.m_tiles + 1) / 2;
-      const double k256 = (double)ceil_div(pm * ceil_div(cols, 256), c256) * 256.0;
-      const double k128 = (double)ceil_div(pm * ceil_div(cols, 128), c128) * 128.0 * 1.10;
+      // time of a tile is set by the bytes it pulls in per K slab: 128 rows of P plus BN rows of Q
+      const double k256 = (double)ceil_div(pm * ceil_div(cols, 256), c256) * (128.0 + 256.0);
+      const double k128 = (double)ceil_div(pm * ceil_div(cols, 128), c128) * (128.0 + 128.0);
       if (k256 <= k128) return launch_gemm2<kFmt, 256>(p_codes, q_codes, g, kbytes, c256, stream);
       return launch_gemm2<kFmt, 128>(p_codes, q_codes, g, kbytes, c128, stream);
     }
   }
   // Tile width: fewer, wider tiles unless narrow ones fill the machine better.
   const int64_t t256 = (int64_t)g.m_tiles * ceil_div(cols, 256), t128 = (int64_t)g.m_tiles * ceil_div(cols, 128);
-  const double cost256 = (double)ceil_div(t256, sms) * 256.0;
-  const double cost128 = (double)ceil_div(t128, sms) * 128.0 * 1.12;
+  const double cost256 = (double)ceil_div(t256, sms) * (128.0 + 256.0);
+  const double cost128 = (double)ceil_div(t128, sms) * (128.0 + 128.0);
   if (cost256 <= cost128) return launch_gemm<kFmt, 256>(p_codes, q_codes, g, kbytes, stream);
   return launch_gemm<kFmt, 128>(p_codes, q_codes, g, kbytes, stream);
 }
