@@ -50,7 +50,21 @@ def _alloc_q(outer, inner, blk, packed, device):
     return codes, sf
 
 
-def _quantize(fmt, x, want_row, want_t, sr, noise, noise_t, seed):
+_colsum_scratch = {}
+
+
+def _scratch(dev, cols):
+    """fp32 scratch of at least `cols` values on `dev` for the fused bias-gradient sums
+    (grown on demand, reused by every call on that device: calls are stream-ordered)."""
+    key = (dev.type, dev.index)
+    buf = _colsum_scratch.get(key)
+    if buf is None or buf.numel() < cols:
+        buf = torch.empty(max(cols, 4096), dtype=torch.float32, device=dev)
+        _colsum_scratch[key] = buf
+    return buf
+
+
+def _quantize(fmt, x, want_row, want_t, sr, noise, noise_t, seed, bias_grad_dtype=None):
     if x.ndim != 2:
         raise ValueError("Input tensor must be 2D for block quantization")
     _need_cuda(x, noise, noise_t)
@@ -65,42 +79,65 @@ def _quantize(fmt, x, want_row, want_t, sr, noise, noise_t, seed):
     if want_t and rows % 32:
         raise ValueError(f"transposed {fmt} quantization needs rows to be a multiple of 32")
     dev = x.device
-    codes = sf = codes_t = sf_t = None
+    codes = sf = codes_t = sf_t = bgrad = None
     with torch.cuda.device(dev):
+        if bias_grad_dtype is not None:
+            bgrad = torch.empty(cols, dtype=bias_grad_dtype, device=dev)
         if want_row:
             codes, sf = _alloc_q(rows, cols, blk, fmt == "nvfp4", dev)
         if want_t:
             codes_t, sf_t = _alloc_q(cols, rows, blk, fmt == "nvfp4", dev)
         if rows == 0 or cols == 0:
+            if bgrad is not None:
+                bgrad.zero_()
+                return codes, sf, codes_t, sf_t, bgrad
             return codes, sf, codes_t, sf_t
         L = _lib.lib()
+        L.fp4t_set_status_word(_lib.ptr(status_word(dev)))
         if fmt == "nvfp4":
             if noise is not None:
                 noise = noise.to(torch.float32).reshape(rows, cols).contiguous()
             if noise_t is not None:
                 noise_t = noise_t.to(torch.float32).reshape(cols, rows).contiguous()
-            rc = L.fp4t_quantize_nvfp4(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
-                                       _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
-                                       int(sr), _lib.ptr(noise), _lib.ptr(noise_t),
-                                       ctypes.c_uint64(seed & (2 ** 64 - 1)), _lib.stream_ptr(dev))
+            if bgrad is None:
+                rc = L.fp4t_quantize_nvfp4(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                           _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                                           int(sr), _lib.ptr(noise), _lib.ptr(noise_t),
+                                           ctypes.c_uint64(seed & (2 ** 64 - 1)), _lib.stream_ptr(dev))
+            else:
+                rc = L.fp4t_quantize_nvfp4_bgrad(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                                 _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                                                 int(sr), _lib.ptr(noise), _lib.ptr(noise_t),
+                                                 ctypes.c_uint64(seed & (2 ** 64 - 1)), _lib.ptr(_scratch(dev, cols)),
+                                                 _lib.ptr(bgrad), _lib.dtype_code(bgrad.dtype), _lib.stream_ptr(dev))
             _lib.check(rc, "fp4t_quantize_nvfp4")
         else:
-            rc = L.fp4t_quantize_mxfp8(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
-                                       _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
-                                       _lib.stream_ptr(dev))
+            if bgrad is None:
+                rc = L.fp4t_quantize_mxfp8(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                           _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                                           _lib.stream_ptr(dev))
+            else:
+                rc = L.fp4t_quantize_mxfp8_bgrad(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                                 _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                                                 _lib.ptr(_scratch(dev, cols)), _lib.ptr(bgrad),
+                                                 _lib.dtype_code(bgrad.dtype), _lib.stream_ptr(dev))
             _lib.check(rc, "fp4t_quantize_mxfp8")
-        LAUNCHES["quantize"] += 1
+        LAUNCHES["quantize"] += 1 if bgrad is None else 2
+    if bgrad is not None:
+        return codes, sf, codes_t, sf_t, bgrad
     return codes, sf, codes_t, sf_t
 
 
-def quantize_nvfp4(x, want_row=True, want_t=False, sr=SR_NONE, noise=None, noise_t=None, seed=0):
-    """-> (codes [R, C/2], sf, codes_t [C, R/2], sf_t); entries not requested are None."""
-    return _quantize("nvfp4", x, want_row, want_t, sr, noise, noise_t, seed)
+def quantize_nvfp4(x, want_row=True, want_t=False, sr=SR_NONE, noise=None, noise_t=None, seed=0,
+                   bias_grad_dtype=None):
+    """-> (codes [R, C/2], sf, codes_t [C, R/2], sf_t); entries not requested are None.
+    With bias_grad_dtype a fifth element is returned: the column sums of x in that dtype."""
+    return _quantize("nvfp4", x, want_row, want_t, sr, noise, noise_t, seed, bias_grad_dtype)
 
 
-def quantize_mxfp8(x, want_row=True, want_t=False):
-    """-> (codes [R, C], sf, codes_t [C, R], sf_t); entries not requested are None."""
-    return _quantize("mxfp8", x, want_row, want_t, SR_NONE, None, None, 0)
+def quantize_mxfp8(x, want_row=True, want_t=False, bias_grad_dtype=None):
+    """-> (codes [R, C], sf, codes_t [C, R], sf_t) (+ column sums of x when bias_grad_dtype is given)."""
+    return _quantize("mxfp8", x, want_row, want_t, SR_NONE, None, None, 0, bias_grad_dtype)
 
 
 def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None):

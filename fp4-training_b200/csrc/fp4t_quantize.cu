@@ -29,6 +29,7 @@ struct QParams {
   uint8_t* sf_t;
   const float* noise;
   const float* noise_t;
+  float* colsum;   // optional fp32 [cols] accumulator of column sums (transposed pass only)
   uint64_t seed;
   int ntx_row;  // scale tiles along k for the row-wise output
   int ntx_col;  // ... for the transposed output
@@ -62,14 +63,229 @@ struct QCfg {
   static constexpr int kKbTile = kTile / kBlk;       // k-blocks per tile edge: 8 or 4
   static constexpr int kSfChunks = kKbTile / 4;      // 512-byte scale tiles per tile edge: 2 or 1
   static constexpr int kSfStage = kSfChunks * 512;   // bytes of one staging buffer
-  static constexpr int kSmemBytes = kQStages * kQTileBytes + 4 * kSfStage + 64 + 128 + 1024;
+  static constexpr int kSmemBytes = kQStages * kQTileBytes + 4 * kSfStage + 64 + 128 + 1024 + 4096;
 };
 
 __device__ __forceinline__ void named_barrier_compute() {
   asm volatile("bar.sync 1, %0;" ::"n"(kQComputeThreads) : "memory");
 }
 
-template <int kFmt, int kSr>
+// Four fp32 values -> four E2M1 codes (e0 in the lowest nibble) with the hardware's stochastic
+// rounding; rbits supplies the random bits of all four conversions.
+__device__ __forceinline__ uint32_t cvt_rs_e2m1x4(float e0, float e1, float e2, float e3, uint32_t rbits) {
+  uint32_t out;
+  asm("{\n\t.reg .b16 h;\n\tcvt.rs.satfinite.e2m1x4.f32 h, {%4, %3, %2, %1}, %5;\n\tcvt.u32.u16 %0, h;\n\t}"
+      : "=r"(out)
+      : "f"(e0), "f"(e1), "f"(e2), "f"(e3), "r"(rbits));
+  return out;
+}
+__device__ __forceinline__ uint32_t hash_bits(uint32_t idx, uint32_t seed_lo, uint32_t seed_hi) {
+  return mix32(idx * 0x9E3779B9u + seed_lo) ^ seed_hi;
+}
+__device__ __forceinline__ float amax8(const uint32_t (&w)[4]) {
+  const float m0 = fmaxf(fabsf(__uint_as_float(w[0] << 16)), fabsf(__uint_as_float(w[0] & 0xFFFF0000u)));
+  const float m1 = fmaxf(fabsf(__uint_as_float(w[1] << 16)), fabsf(__uint_as_float(w[1] & 0xFFFF0000u)));
+  const float m2 = fmaxf(fabsf(__uint_as_float(w[2] << 16)), fabsf(__uint_as_float(w[2] & 0xFFFF0000u)));
+  const float m3 = fmaxf(fabsf(__uint_as_float(w[3] << 16)), fabsf(__uint_as_float(w[3] & 0xFFFF0000u)));
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+struct TileCtx {
+  const uint8_t* tile;      // 128 x 128 bf16, 256-byte rows
+  uint8_t* sf_row_s;
+  uint8_t* sf_col_s;
+  float* colsum_s;          // [4][128] partial column sums of this tile
+  const float2* scale_tab;
+  int64_t row0, col0;
+  int tid;
+};
+
+// ---- row-wise pass: a thread handles 8 consecutive elements of a row, 8 times ----------
+template <int kFmt, int kSr, bool kEdge>
+__device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
+  using C = QCfg<kFmt>;
+  const int r_base = c.tid >> 4, cv = c.tid & 15;
+  const int64_t gc = c.col0 + cv * 8;
+  const int kb = (cv * 8) / C::kBlk;
+  const bool col_ok = !kEdge || gc < p.cols;
+  const int64_t code_pitch = kFmt == kNvfp4 ? (p.cols >> 1) : p.cols;
+  uint8_t* out = p.codes + (c.row0 + r_base) * code_pitch + (kFmt == kNvfp4 ? (gc >> 1) : gc);
+  const int64_t out_step = 16 * code_pitch;
+  const uint8_t* src = c.tile + r_base * 256 + cv * 16;
+  const uint32_t seed_lo = (uint32_t)p.seed, seed_hi = (uint32_t)(p.seed >> 32);
+#pragma unroll 4
+  for (int it = 0; it < 8; ++it, out += out_step) {
+    const int r = it * 16 + r_base;
+    const int64_t gr = c.row0 + r;
+    const uint4 v = *reinterpret_cast<const uint4*>(src + it * 16 * 256);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float amax = amax8(w);
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    if (kFmt == kMxfp8) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const bool valid = !kEdge || (col_ok && gr < p.rows);
+    if (kFmt == kNvfp4) {
+      float s, rcp;
+      nvfp4_scale_from_table(c.scale_tab, amax, s, rcp);
+      const uint64_t rcp2 = pack2(rcp, rcp), neg2 = pack2(-s, -s);
+      float y[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[j]), neg2, rcp2), y[2 * j], y[2 * j + 1]);
+      uint32_t packed;
+      if (kSr == FP4T_SR_HASH) {
+        const uint32_t e0 = (uint32_t)((gr * p.cols + gc) >> 2);
+        packed = cvt_rs_e2m1x4(y[0], y[1], y[2], y[3], hash_bits(e0, seed_lo, seed_hi)) |
+                 (cvt_rs_e2m1x4(y[4], y[5], y[6], y[7], hash_bits(e0 + 1, seed_lo, seed_hi)) << 16);
+      } else {
+        if (kSr == FP4T_SR_NOISE) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) y[j] = sr_round(y[j], valid ? __ldg(p.noise + gr * p.cols + gc + j) : 0.5f);
+        }
+        packed = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
+      }
+      if (valid) *reinterpret_cast<uint32_t*>(out) = packed;
+      if ((cv & 1) == 0)
+        c.sf_row_s[(kb >> 2) * 512 + sf_tile_offset(r, kb)] = valid ? (uint8_t)e4m3_byte_of_scale(s) : (uint8_t)0;
+    } else {
+      const uint32_t sb = mx_scale_byte(amax);
+      const float inv = mx_inv_scale(sb);
+      uint32_t o[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t w0 = w[2 * h], w1 = w[2 * h + 1];
+        o[h] = mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 << 16), inv, 0.0f),
+                                   fmaf(__uint_as_float(w0 & 0xFFFF0000u), inv, 0.0f)) |
+               (mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w1 << 16), inv, 0.0f),
+                                    fmaf(__uint_as_float(w1 & 0xFFFF0000u), inv, 0.0f)) << 16);
+      }
+      if (valid) *reinterpret_cast<uint2*>(out) = make_uint2(o[0], o[1]);
+      if ((cv & 3) == 0) c.sf_row_s[sf_tile_offset(r, kb)] = valid ? (uint8_t)sb : (uint8_t)0;
+    }
+  }
+}
+
+// ---- transposed pass: a thread handles 2 adjacent columns x 32 rows --------------------
+template <int kFmt, int kSr, bool kEdge, bool kColsum>
+__device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
+  const int cp = c.tid & 63, q = c.tid >> 6;
+  const int64_t gr0 = c.row0 + q * 32, gcA = c.col0 + 2 * cp;
+  const bool rows_ok = !kEdge || gr0 < p.rows;       // rows % 32 == 0: all 32 rows in or out
+  const bool okA = rows_ok && (!kEdge || gcA < p.cols), okB = rows_ok && (!kEdge || gcA + 1 < p.cols);
+  const uint32_t* col_words = reinterpret_cast<const uint32_t*>(c.tile + (q * 32) * 256) + cp;
+  uint64_t sum2 = 0;   // packed fp32 (0, 0)
+  if (kFmt == kNvfp4) {
+    uint32_t outA[4], outB[4];
+    const uint32_t seed_lo = (uint32_t)p.seed ^ 0x5BD1E995u, seed_hi = (uint32_t)(p.seed >> 32);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) w[j] = col_words[(h * 16 + j) * 64];
+      float mA[4], mB[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mA[j] = fmaxf(fmaxf(fabsf(__uint_as_float(w[4 * j] << 16)), fabsf(__uint_as_float(w[4 * j + 1] << 16))),
+                      fmaxf(fabsf(__uint_as_float(w[4 * j + 2] << 16)), fabsf(__uint_as_float(w[4 * j + 3] << 16))));
+        mB[j] = fmaxf(fmaxf(fabsf(__uint_as_float(w[4 * j] & 0xFFFF0000u)), fabsf(__uint_as_float(w[4 * j + 1] & 0xFFFF0000u))),
+                      fmaxf(fabsf(__uint_as_float(w[4 * j + 2] & 0xFFFF0000u)), fabsf(__uint_as_float(w[4 * j + 3] & 0xFFFF0000u))));
+      }
+      const float amA = fmaxf(fmaxf(mA[0], mA[1]), fmaxf(mA[2], mA[3]));
+      const float amB = fmaxf(fmaxf(mB[0], mB[1]), fmaxf(mB[2], mB[3]));
+      float sA, sB, rA, rB;
+      nvfp4_scale_from_table(c.scale_tab, amA, sA, rA);
+      nvfp4_scale_from_table(c.scale_tab, amB, sB, rB);
+      const uint64_t rcp2 = pack2(rA, rB), neg2 = pack2(-sA, -sB);
+#pragma unroll
+      for (int g8 = 0; g8 < 2; ++g8) {
+        float yA[8], yB[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint64_t x2 = bf16x2_to_f32x2(w[g8 * 8 + j]);
+          if (kColsum) sum2 = add2(sum2, x2);
+          unpack2(div_corrected2(x2, neg2, rcp2), yA[j], yB[j]);
+        }
+        uint32_t a8, b8;
+        if (kSr == FP4T_SR_HASH) {
+          const uint32_t rg = (uint32_t)((gr0 + h * 16 + g8 * 8) >> 2);
+          const uint32_t i0 = rg * (uint32_t)p.cols + (uint32_t)gcA;
+          const uint32_t i1 = i0 + (uint32_t)p.cols;
+          a8 = cvt_rs_e2m1x4(yA[0], yA[1], yA[2], yA[3], hash_bits(i0, seed_lo, seed_hi)) |
+               (cvt_rs_e2m1x4(yA[4], yA[5], yA[6], yA[7], hash_bits(i1, seed_lo, seed_hi)) << 16);
+          b8 = cvt_rs_e2m1x4(yB[0], yB[1], yB[2], yB[3], hash_bits(i0 + 1, seed_lo, seed_hi)) |
+               (cvt_rs_e2m1x4(yB[4], yB[5], yB[6], yB[7], hash_bits(i1 + 1, seed_lo, seed_hi)) << 16);
+        } else {
+          if (kSr == FP4T_SR_NOISE) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int64_t gr = gr0 + h * 16 + g8 * 8 + j;
+              yA[j] = sr_round(yA[j], okA ? __ldg(p.noise_t + gcA * p.rows + gr) : 0.5f);
+              yB[j] = sr_round(yB[j], okB ? __ldg(p.noise_t + (gcA + 1) * p.rows + gr) : 0.5f);
+            }
+          }
+          a8 = cvt_e2m1x8(yA[0], yA[1], yA[2], yA[3], yA[4], yA[5], yA[6], yA[7]);
+          b8 = cvt_e2m1x8(yB[0], yB[1], yB[2], yB[3], yB[4], yB[5], yB[6], yB[7]);
+        }
+        outA[2 * h + g8] = a8;
+        outB[2 * h + g8] = b8;
+      }
+      const int kb = q * 2 + h;
+      c.sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp, kb)] = okA ? (uint8_t)e4m3_byte_of_scale(sA) : (uint8_t)0;
+      c.sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp + 1, kb)] = okB ? (uint8_t)e4m3_byte_of_scale(sB) : (uint8_t)0;
+    }
+    if (okA)
+      *reinterpret_cast<uint4*>(p.codes_t + gcA * (p.rows >> 1) + (gr0 >> 1)) =
+          make_uint4(outA[0], outA[1], outA[2], outA[3]);
+    if (okB)
+      *reinterpret_cast<uint4*>(p.codes_t + (gcA + 1) * (p.rows >> 1) + (gr0 >> 1)) =
+          make_uint4(outB[0], outB[1], outB[2], outB[3]);
+  } else {
+    uint32_t w[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = col_words[j * 64];
+    float amA = 0.0f, amB = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      amA = fmaxf(amA, fmaxf(fabsf(__uint_as_float(w[j] << 16)), fabsf(__uint_as_float(w[j + 1] << 16))));
+      amB = fmaxf(amB, fmaxf(fabsf(__uint_as_float(w[j] & 0xFFFF0000u)), fabsf(__uint_as_float(w[j + 1] & 0xFFFF0000u))));
+    }
+    const uint32_t sbA = mx_scale_byte(amA), sbB = mx_scale_byte(amB);
+    const float invA = mx_inv_scale(sbA), invB = mx_inv_scale(sbB);
+    uint32_t oA[8], oB[8];
+#pragma unroll
+    for (int g4 = 0; g4 < 8; ++g4) {
+      uint32_t a = 0, b = 0;
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const uint32_t w0 = w[g4 * 4 + j], w1 = w[g4 * 4 + j + 1];
+        if (kColsum) sum2 = add2(add2(sum2, bf16x2_to_f32x2(w0)), bf16x2_to_f32x2(w1));
+        a |= mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 << 16), invA, 0.0f),
+                                 fmaf(__uint_as_float(w1 << 16), invA, 0.0f)) << (8 * j);
+        b |= mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 & 0xFFFF0000u), invB, 0.0f),
+                                 fmaf(__uint_as_float(w1 & 0xFFFF0000u), invB, 0.0f)) << (8 * j);
+      }
+      oA[g4] = a;
+      oB[g4] = b;
+    }
+    if (okA) {
+      uint4* dst = reinterpret_cast<uint4*>(p.codes_t + gcA * p.rows + gr0);
+      dst[0] = make_uint4(oA[0], oA[1], oA[2], oA[3]);
+      dst[1] = make_uint4(oA[4], oA[5], oA[6], oA[7]);
+    }
+    if (okB) {
+      uint4* dst = reinterpret_cast<uint4*>(p.codes_t + (gcA + 1) * p.rows + gr0);
+      dst[0] = make_uint4(oB[0], oB[1], oB[2], oB[3]);
+      dst[1] = make_uint4(oB[4], oB[5], oB[6], oB[7]);
+    }
+    c.sf_col_s[sf_tile_offset(2 * cp, q)] = okA ? (uint8_t)sbA : (uint8_t)0;
+    c.sf_col_s[sf_tile_offset(2 * cp + 1, q)] = okB ? (uint8_t)sbB : (uint8_t)0;
+  }
+  if (kColsum) {
+    float sa, sb;
+    unpack2(sum2, sa, sb);
+    *reinterpret_cast<float2*>(c.colsum_s + q * kTile + 2 * cp) = make_float2(sa, sb);
+  }
+}
+
+template <int kFmt, int kSr, bool kColsum>
 __global__ void __launch_bounds__(kQThreads, 2)
 quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, const int tiles_x,
                     const int num_tiles, int32_t* status) {
@@ -83,6 +299,7 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
   const uint32_t bar_empty = bar_full + 8 * kQStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kQStages);
   float2* scale_tab = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(bars) + 64);
+  float* colsum_stage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 64 + 1024);   // [2][4][128]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -127,168 +344,23 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
   int buf = 0;
   for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
     const int ty = t / tiles_x, tx = t - ty * tiles_x;
-    const int64_t row0 = (int64_t)ty * kTile, col0 = (int64_t)tx * kTile;
+    TileCtx c;
+    c.row0 = (int64_t)ty * kTile;
+    c.col0 = (int64_t)tx * kTile;
     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 12)) break;
-    const uint8_t* tile = gen + stage * kQTileBytes;
-    uint8_t* sf_row_s = sf_stage + buf * 2 * C::kSfStage;
-    uint8_t* sf_col_s = sf_row_s + C::kSfStage;
-
-    // ---- row-wise pass: thread handles 8 elements of a row, 8 times -------------------
-    if (want_row) {
-#pragma unroll 2
-      for (int it = 0; it < 8; ++it) {
-        const int vi = it * kQComputeThreads + tid;
-        const int r = vi >> 4, cv = vi & 15;
-        const int64_t gr = row0 + r, gc = col0 + cv * 8;
-        const uint4 v = *reinterpret_cast<const uint4*>(tile + r * 256 + cv * 16);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        float amax = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          amax = fmaxf(amax, fabsf(__uint_as_float(w[j] << 16)));
-          amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
-        }
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-        if (kFmt == kMxfp8) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-        const bool valid = gr < p.rows && gc < p.cols;
-        const int kb = (cv * 8) / C::kBlk;
-        if (kFmt == kNvfp4) {
-          float s, rcp;
-          nvfp4_scale_from_table(scale_tab, amax, s, rcp);
-          const uint64_t rcp2 = pack2(rcp, rcp), neg2 = pack2(-s, -s);
-          float y[8];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[j]), neg2, rcp2), y[2 * j], y[2 * j + 1]);
-          if (kSr == FP4T_SR_NOISE) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = sr_round(y[j], valid ? __ldg(p.noise + gr * p.cols + gc + j) : 0.5f);
-          } else if (kSr == FP4T_SR_HASH) {
-            const uint32_t e0 = (uint32_t)((gr * p.cols + gc) >> 1);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t h = mix32((e0 + j) * 0x9E3779B9u + (uint32_t)p.seed) ^ (uint32_t)(p.seed >> 32);
-              y[2 * j] = sr_round_bits(y[2 * j], h & 0xFFFFu);
-              y[2 * j + 1] = sr_round_bits(y[2 * j + 1], h >> 16);
-            }
-          }
-          const uint32_t packed = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
-          if (valid) *reinterpret_cast<uint32_t*>(p.codes + gr * (p.cols >> 1) + (gc >> 1)) = packed;
-          if ((cv & 1) == 0)
-            sf_row_s[(kb >> 2) * 512 + sf_tile_offset(r, kb)] = valid ? (uint8_t)e4m3_byte_of_scale(s) : (uint8_t)0;
-        } else {
-          const uint32_t sb = mx_scale_byte(amax);
-          const float inv = mx_inv_scale(sb);
-          uint32_t o[2] = {0u, 0u};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float y0 = fmaf(__uint_as_float(w[j] << 16), inv, 0.0f);
-            const float y1 = fmaf(__uint_as_float(w[j] & 0xFFFF0000u), inv, 0.0f);
-            o[j >> 1] |= mx_e4m3x2_from_bf16(y0, y1) << (16 * (j & 1));
-          }
-          if (valid) *reinterpret_cast<uint2*>(p.codes + gr * p.cols + gc) = make_uint2(o[0], o[1]);
-          if ((cv & 3) == 0) sf_row_s[sf_tile_offset(r, kb)] = valid ? (uint8_t)sb : (uint8_t)0;
-        }
-      }
-    }
-
-    // ---- transposed pass: thread handles 2 adjacent columns x 32 rows --------------------
-    if (want_col) {
-      const int cp = tid & 63, q = tid >> 6;
-      const int64_t gr0 = row0 + q * 32, gcA = col0 + 2 * cp;
-      const bool rows_ok = gr0 < p.rows;             // rows % 32 == 0: all 32 rows in or out
-      const bool okA = rows_ok && gcA < p.cols, okB = rows_ok && gcA + 1 < p.cols;
-      const uint32_t* col_words = reinterpret_cast<const uint32_t*>(tile + (q * 32) * 256) + cp;
-      if (kFmt == kNvfp4) {
-        uint32_t outA[4], outB[4];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) w[j] = col_words[(h * 16 + j) * 64];
-          float amA = 0.0f, amB = 0.0f;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            amA = fmaxf(amA, fabsf(__uint_as_float(w[j] << 16)));
-            amB = fmaxf(amB, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
-          }
-          float sA, sB, rA, rB;
-          nvfp4_scale_from_table(scale_tab, amA, sA, rA);
-          nvfp4_scale_from_table(scale_tab, amB, sB, rB);
-          const uint64_t rcp2 = pack2(rA, rB), neg2 = pack2(-sA, -sB);
-          float yA[16], yB[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[j]), neg2, rcp2), yA[j], yB[j]);
-          if (kSr == FP4T_SR_NOISE) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int64_t gr = gr0 + h * 16 + j;
-              yA[j] = sr_round(yA[j], okA ? __ldg(p.noise_t + gcA * p.rows + gr) : 0.5f);
-              yB[j] = sr_round(yB[j], okB ? __ldg(p.noise_t + (gcA + 1) * p.rows + gr) : 0.5f);
-            }
-          } else if (kSr == FP4T_SR_HASH) {
-            const uint32_t seed_lo = (uint32_t)p.seed ^ 0x5BD1E995u, seed_hi = (uint32_t)(p.seed >> 32);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const uint32_t e = (uint32_t)((gr0 + h * 16 + j) * (p.cols >> 1) + (gcA >> 1));
-              const uint32_t hsh = mix32(e * 0x9E3779B9u + seed_lo) ^ seed_hi;
-              yA[j] = sr_round_bits(yA[j], hsh & 0xFFFFu);
-              yB[j] = sr_round_bits(yB[j], hsh >> 16);
-            }
-          }
-          outA[2 * h] = cvt_e2m1x8(yA[0], yA[1], yA[2], yA[3], yA[4], yA[5], yA[6], yA[7]);
-          outA[2 * h + 1] = cvt_e2m1x8(yA[8], yA[9], yA[10], yA[11], yA[12], yA[13], yA[14], yA[15]);
-          outB[2 * h] = cvt_e2m1x8(yB[0], yB[1], yB[2], yB[3], yB[4], yB[5], yB[6], yB[7]);
-          outB[2 * h + 1] = cvt_e2m1x8(yB[8], yB[9], yB[10], yB[11], yB[12], yB[13], yB[14], yB[15]);
-          const int kb = q * 2 + h;
-          sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp, kb)] = okA ? (uint8_t)e4m3_byte_of_scale(sA) : (uint8_t)0;
-          sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp + 1, kb)] = okB ? (uint8_t)e4m3_byte_of_scale(sB) : (uint8_t)0;
-        }
-        if (okA)
-          *reinterpret_cast<uint4*>(p.codes_t + gcA * (p.rows >> 1) + (gr0 >> 1)) =
-              make_uint4(outA[0], outA[1], outA[2], outA[3]);
-        if (okB)
-          *reinterpret_cast<uint4*>(p.codes_t + (gcA + 1) * (p.rows >> 1) + (gr0 >> 1)) =
-              make_uint4(outB[0], outB[1], outB[2], outB[3]);
-      } else {
-        uint32_t w[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) w[j] = col_words[j * 64];
-        float amA = 0.0f, amB = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          amA = fmaxf(amA, fabsf(__uint_as_float(w[j] << 16)));
-          amB = fmaxf(amB, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
-        }
-        const uint32_t sbA = mx_scale_byte(amA), sbB = mx_scale_byte(amB);
-        const float invA = mx_inv_scale(sbA), invB = mx_inv_scale(sbB);
-        uint32_t oA[8], oB[8];
-#pragma unroll
-        for (int g4 = 0; g4 < 8; ++g4) {
-          uint32_t a = 0, b = 0;
-#pragma unroll
-          for (int j = 0; j < 4; j += 2) {
-            const uint32_t w0 = w[g4 * 4 + j], w1 = w[g4 * 4 + j + 1];
-            a |= mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 << 16), invA, 0.0f),
-                                     fmaf(__uint_as_float(w1 << 16), invA, 0.0f)) << (8 * j);
-            b |= mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 & 0xFFFF0000u), invB, 0.0f),
-                                     fmaf(__uint_as_float(w1 & 0xFFFF0000u), invB, 0.0f)) << (8 * j);
-          }
-          oA[g4] = a;
-          oB[g4] = b;
-        }
-        if (okA) {
-          uint4* dst = reinterpret_cast<uint4*>(p.codes_t + gcA * p.rows + gr0);
-          dst[0] = make_uint4(oA[0], oA[1], oA[2], oA[3]);
-          dst[1] = make_uint4(oA[4], oA[5], oA[6], oA[7]);
-        }
-        if (okB) {
-          uint4* dst = reinterpret_cast<uint4*>(p.codes_t + (gcA + 1) * p.rows + gr0);
-          dst[0] = make_uint4(oB[0], oB[1], oB[2], oB[3]);
-          dst[1] = make_uint4(oB[4], oB[5], oB[6], oB[7]);
-        }
-        sf_col_s[sf_tile_offset(2 * cp, q)] = okA ? (uint8_t)sbA : (uint8_t)0;
-        sf_col_s[sf_tile_offset(2 * cp + 1, q)] = okB ? (uint8_t)sbB : (uint8_t)0;
-      }
+    c.tile = gen + stage * kQTileBytes;
+    c.sf_row_s = sf_stage + buf * 2 * C::kSfStage;
+    c.sf_col_s = c.sf_row_s + C::kSfStage;
+    c.colsum_s = colsum_stage + buf * 4 * kTile;
+    c.scale_tab = scale_tab;
+    c.tid = tid;
+    const bool interior = c.row0 + kTile <= p.rows && c.col0 + kTile <= p.cols;
+    if (interior) {
+      if (want_row) row_pass<kFmt, kSr, false>(p, c);
+      if (want_col) col_pass<kFmt, kSr, false, kColsum>(p, c);
+    } else {
+      if (want_row) row_pass<kFmt, kSr, true>(p, c);
+      if (want_col) col_pass<kFmt, kSr, true, kColsum>(p, c);
     }
 
     // the tile is consumed: hand the stage back to the producer
@@ -304,7 +376,7 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
       const int64_t stx = (int64_t)tx * C::kSfChunks + chunk;
       if (stx < p.ntx_row) {
         uint8_t* dst = p.sf + ((int64_t)ty * p.ntx_row + stx) * 512;
-        reinterpret_cast<uint4*>(dst)[tid & 31] = reinterpret_cast<const uint4*>(sf_row_s)[tid];
+        reinterpret_cast<uint4*>(dst)[tid & 31] = reinterpret_cast<const uint4*>(c.sf_row_s)[tid];
       }
     }
     if (want_col && tid >= 64 && tid < 64 + kVecs) {
@@ -313,7 +385,14 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
       const int64_t stx = (int64_t)ty * C::kSfChunks + chunk;
       if (stx < p.ntx_col) {
         uint8_t* dst = p.sf_t + ((int64_t)tx * p.ntx_col + stx) * 512;
-        reinterpret_cast<uint4*>(dst)[u & 31] = reinterpret_cast<const uint4*>(sf_col_s)[u];
+        reinterpret_cast<uint4*>(dst)[u & 31] = reinterpret_cast<const uint4*>(c.sf_col_s)[u];
+      }
+    }
+    if (kColsum && tid >= 128) {   // column sums of the tile: 4 row quarters -> one atomic per column
+      const int col = tid - 128;
+      if (c.col0 + col < p.cols) {
+        const float* cs = c.colsum_s + col;
+        atomicAdd(p.colsum + c.col0 + col, (cs[0] + cs[kTile]) + (cs[2 * kTile] + cs[3 * kTile]));
       }
     }
     buf ^= 1;
@@ -407,10 +486,36 @@ int launch_generic(const QParams& p, int x_dtype, int sr, cudaStream_t stream) {
   return FP4T_OK;
 }
 
+// Column sums of x [rows, cols] added into an fp32 accumulator: one thread per column.
+template <typename TIn>
+__global__ void colsum_generic_kernel(const TIn* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+                                      float* __restrict__ colsum) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.0f;
+  for (int64_t r = 0; r < rows; ++r) acc += (float)x[r * ld + c];
+  colsum[c] += acc;
+}
+
+// fp32 accumulator -> bias gradient in the caller's dtype.
+__global__ void colsum_finalize_kernel(const float* __restrict__ colsum, void* __restrict__ out, int out_f32,
+                                       int64_t cols) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  if (out_f32) static_cast<float*>(out)[c] = colsum[c];
+  else static_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(colsum[c]);
+}
+
+template <int kFmt>
+int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, void* codes, void* sf,
+                   void* codes_t, void* sf_t, int sr_mode, const float* noise, const float* noise_t, uint64_t seed,
+                   float* colsum_scratch, void* bias_grad, int bias_grad_dtype, cudaStream_t stream);
+
 template <int kFmt>
 int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
                       void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
-                      const float* noise, const float* noise_t, uint64_t seed, cudaStream_t stream) {
+                      const float* noise, const float* noise_t, uint64_t seed, float* colsum,
+                      cudaStream_t stream) {
   constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
   const char* name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4" : "fp4t_quantize_mxfp8";
   FP4T_REQUIRE(x != nullptr, "%s: x is null", name);
@@ -433,7 +538,7 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   p.x = x; p.rows = rows; p.cols = cols; p.ld = ld;
   p.codes = static_cast<uint8_t*>(codes); p.sf = static_cast<uint8_t*>(sf);
   p.codes_t = static_cast<uint8_t*>(codes_t); p.sf_t = static_cast<uint8_t*>(sf_t);
-  p.noise = noise; p.noise_t = noise_t; p.seed = seed;
+  p.noise = noise; p.noise_t = noise_t; p.seed = seed; p.colsum = colsum;
   p.ntx_row = (int)ceil_div(ceil_div(cols, kBlk), 4);
   p.ntx_col = (int)ceil_div(ceil_div(rows, kBlk), 4);
 
@@ -443,7 +548,21 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
                     (codes_t == nullptr || reinterpret_cast<uintptr_t>(codes_t) % 16 == 0) &&
                     (sf == nullptr || reinterpret_cast<uintptr_t>(sf) % 16 == 0) &&
                     (sf_t == nullptr || reinterpret_cast<uintptr_t>(sf_t) % 16 == 0);
-  if (!fast) return launch_generic<kFmt>(p, x_dtype, sr_mode, stream);
+  if (!fast || (colsum != nullptr && codes_t == nullptr)) {
+    // column sums ride on the transposed pass of the tiled kernel; otherwise a plain kernel adds them
+    if (colsum != nullptr) {
+      const int threads = 256;
+      const int64_t blocks = ceil_div(cols, threads);
+      if (x_dtype == FP4T_DT_BF16)
+        colsum_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(x), rows, cols, ld, colsum);
+      else
+        colsum_generic_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(static_cast<const float*>(x), rows,
+                                                                                cols, ld, colsum);
+      p.colsum = nullptr;
+    }
+    if (!fast) return launch_generic<kFmt>(p, x_dtype, sr_mode, stream);
+  }
 
   const int sms = sm_count();
   if (sms < 0) {
@@ -459,11 +578,16 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   if (rc != FP4T_OK) return rc;
   const int grid = num_tiles < 2 * sms ? num_tiles : 2 * sms;
   int32_t* status = current_status_word();
-#define FP4T_LAUNCH_Q(FMT, SR)                                                                             \
+#define FP4T_LAUNCH_Q2(FMT, SR, CS)                                                                        \
   do {                                                                                                     \
-    auto kern = quantize_tma_kernel<FMT, SR>;                                                              \
+    auto kern = quantize_tma_kernel<FMT, SR, CS>;                                                          \
     FP4T_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<FMT>::kSmemBytes)); \
     kern<<<grid, kQThreads, QCfg<FMT>::kSmemBytes, stream>>>(map_x, p, (int)tiles_x, num_tiles, status);   \
+  } while (0)
+#define FP4T_LAUNCH_Q(FMT, SR)                  \
+  do {                                          \
+    if (p.colsum != nullptr) FP4T_LAUNCH_Q2(FMT, SR, true); \
+    else FP4T_LAUNCH_Q2(FMT, SR, false);        \
   } while (0)
   if (kFmt == kMxfp8) {
     FP4T_LAUNCH_Q(kMxfp8, FP4T_SR_NONE);
@@ -475,6 +599,29 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
     FP4T_LAUNCH_Q(kNvfp4, FP4T_SR_HASH);
   }
 #undef FP4T_LAUNCH_Q
+#undef FP4T_LAUNCH_Q2
+  FP4T_CUDA(cudaGetLastError());
+  return FP4T_OK;
+}
+
+template <int kFmt>
+int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, void* codes, void* sf,
+                   void* codes_t, void* sf_t, int sr_mode, const float* noise, const float* noise_t, uint64_t seed,
+                   float* colsum_scratch, void* bias_grad, int bias_grad_dtype, cudaStream_t stream) {
+  const char* name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4_bgrad" : "fp4t_quantize_mxfp8_bgrad";
+  FP4T_REQUIRE(colsum_scratch != nullptr && bias_grad != nullptr, "%s: scratch and bias_grad must be given", name);
+  FP4T_REQUIRE(reinterpret_cast<uintptr_t>(colsum_scratch) % 4 == 0, "%s: scratch must be 4-byte aligned", name);
+  FP4T_REQUIRE(bias_grad_dtype == FP4T_DT_BF16 || bias_grad_dtype == FP4T_DT_F32, "%s: bad bias_grad dtype", name);
+  FP4T_REQUIRE(cols >= 0, "%s: negative cols", name);
+  if (cols == 0) return FP4T_OK;
+  FP4T_CUDA(cudaMemsetAsync(colsum_scratch, 0, (size_t)cols * sizeof(float), stream));
+  if (rows > 0) {
+    const int rc = quantize_dispatch<kFmt>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise,
+                                           noise_t, seed, colsum_scratch, stream);
+    if (rc != FP4T_OK) return rc;
+  }
+  colsum_finalize_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, stream>>>(colsum_scratch, bias_grad,
+                                                                           bias_grad_dtype == FP4T_DT_F32, cols);
   FP4T_CUDA(cudaGetLastError());
   return FP4T_OK;
 }
@@ -482,12 +629,31 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
 }  // namespace
 }  // namespace fp4t
 
+extern "C" int fp4t_quantize_nvfp4_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                         void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
+                                         const float* noise, const float* noise_t, uint64_t seed,
+                                         float* colsum_scratch, void* bias_grad, int bias_grad_dtype,
+                                         fp4t_stream_t stream) {
+  return fp4t::quantize_bgrad<fp4t::kNvfp4>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise,
+                                            noise_t, seed, colsum_scratch, bias_grad, bias_grad_dtype,
+                                            reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fp4t_quantize_mxfp8_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                         void* codes, void* sf, void* codes_t, void* sf_t,
+                                         float* colsum_scratch, void* bias_grad, int bias_grad_dtype,
+                                         fp4t_stream_t stream) {
+  return fp4t::quantize_bgrad<fp4t::kMxfp8>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, FP4T_SR_NONE,
+                                            nullptr, nullptr, 0, colsum_scratch, bias_grad, bias_grad_dtype,
+                                            reinterpret_cast<cudaStream_t>(stream));
+}
+
 extern "C" int fp4t_quantize_nvfp4(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
                                    void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
                                    const float* noise, const float* noise_t, uint64_t seed,
                                    fp4t_stream_t stream) {
   return fp4t::quantize_dispatch<fp4t::kNvfp4>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t,
-                                               sr_mode, noise, noise_t, seed,
+                                               sr_mode, noise, noise_t, seed, nullptr,
                                                reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -495,6 +661,6 @@ extern "C" int fp4t_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int
                                    void* codes, void* sf, void* codes_t, void* sf_t,
                                    fp4t_stream_t stream) {
   return fp4t::quantize_dispatch<fp4t::kMxfp8>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t,
-                                               FP4T_SR_NONE, nullptr, nullptr, 0,
+                                               FP4T_SR_NONE, nullptr, nullptr, 0, nullptr,
                                                reinterpret_cast<cudaStream_t>(stream));
 }

@@ -40,18 +40,29 @@ def is_stock(quant, expected) -> bool:
     return True
 
 
-def quant_pair(fmt, t, want_row, want_t, sr=False):
-    """(codes, sf, codes_t, sf_t) of tensor t in format fmt ('nvfp4' | 'mxfp8')."""
+def quant_pair(fmt, t, want_row, want_t, sr=False, bias_grad_dtype=None):
+    """(codes, sf, codes_t, sf_t) of tensor t in format fmt ('nvfp4' | 'mxfp8'); with
+    bias_grad_dtype a fifth element, the column sums of t, computed in the same pass."""
     if fmt == "mxfp8":
-        return Q.mxfp8_fused(t, want_row, want_t)
+        return Q.mxfp8_fused(t, want_row, want_t, bias_grad_dtype)
     if not sr:
-        return Q.nvfp4_fused(t, want_row, want_t)
+        return Q.nvfp4_fused(t, want_row, want_t, bias_grad_dtype=bias_grad_dtype)
     if parity_mode():
         r, c = t.shape
         noise = torch.rand(r, c // 16, 16, device=t.device) if want_row else None
         noise_t = torch.rand(c, r // 16, 16, device=t.device) if want_t else None
-        return Q.nvfp4_fused(t, want_row, want_t, sr=True, noise=noise, noise_t=noise_t)
-    return Q.nvfp4_fused(t, want_row, want_t, sr=True)
+        return Q.nvfp4_fused(t, want_row, want_t, sr=True, noise=noise, noise_t=noise_t,
+                             bias_grad_dtype=bias_grad_dtype)
+    return Q.nvfp4_fused(t, want_row, want_t, sr=True, bias_grad_dtype=bias_grad_dtype)
+
+
+def grad_quant(fmt, grad_Y, need_dx, need_dw, need_db, sr):
+    """Quantize dY for dgrad / wgrad and, if asked, take the bias gradient in the same pass.
+    -> (codes, sf, codes_t, sf_t, grad_b or None)."""
+    if need_db and (need_dx or need_dw):
+        return quant_pair(fmt, grad_Y, need_dx, need_dw, sr=sr, bias_grad_dtype=grad_Y.dtype)
+    out = quant_pair(fmt, grad_Y, need_dx, need_dw, sr=sr) if (need_dx or need_dw) else (None,) * 4
+    return (*out, grad_Y.sum(dim=0) if need_db else None)
 
 
 def gemm(fmt, p, p_sf, q, q_sf, bias, out_dtype):

@@ -30,19 +30,21 @@ STOCK = OrderedDict([
 
 
 def mxfp8_backward(ctx, grad_Y, W, X, Wt, Xt):
-    """dgrad / wgrad in MXFP8.  Wt / Xt are (codes_t, sf_t) pairs or None."""
+    """dgrad / wgrad / bias grad in MXFP8.  Wt / Xt are (codes_t, sf_t) pairs or None.
+    -> (grad_X, grad_W, grad_b)."""
     need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
     grad_X = grad_W = None
     if need_dx and Wt is None:
         Wt = F.quant_pair("mxfp8", W.to(grad_Y.dtype), False, True)[2:]
     if need_dw and Xt is None:
         Xt = F.quant_pair("mxfp8", X.to(grad_Y.dtype), False, True)[2:]
-    Gc, Gsf, Gtc, Gtsf = F.quant_pair("mxfp8", grad_Y, need_dx, need_dw)
+    need_db = ctx.has_bias and ctx.needs_input_grad[2]
+    Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("mxfp8", grad_Y, need_dx, need_dw, need_db, sr=False)
     if need_dx:
         grad_X = F.gemm("mxfp8", Gc, Gsf, Wt[0], Wt[1], None, grad_Y.dtype)
     if need_dw:
         grad_W = F.gemm("mxfp8", Gtc, Gtsf, Xt[0], Xt[1], None, grad_Y.dtype)
-    return grad_X, grad_W
+    return grad_X, grad_W, grad_b
 
 
 def mxfp8_backward_unfused(ctx, grad_Y, X, W):
@@ -91,12 +93,12 @@ class Mxfp8MatMul(torch.autograd.Function):
         if not ctx.fused:
             X, W = ctx.saved_tensors
             grad_X, grad_W = mxfp8_backward_unfused(ctx, grad_Y, X, W)
+            grad_b = grad_Y.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
         else:
             Wtc, Wtsf, Xtc, Xtsf, W, X = ctx.saved_tensors
-            grad_X, grad_W = mxfp8_backward(ctx, grad_Y, W, X,
-                                            None if Wtc is None else (Wtc, Wtsf),
-                                            None if Xtc is None else (Xtc, Xtsf))
-        grad_b = grad_Y.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+            grad_X, grad_W, grad_b = mxfp8_backward(ctx, grad_Y, W, X,
+                                                    None if Wtc is None else (Wtc, Wtsf),
+                                                    None if Xtc is None else (Xtc, Xtsf))
         return grad_X, grad_W, grad_b, None
 
 

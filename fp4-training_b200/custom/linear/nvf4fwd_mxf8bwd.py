@@ -50,9 +50,9 @@ class FwdNvfp4BwdMxfp8Matmul(torch.autograd.Function):
         grad_Y = grad_Y.contiguous()
         if not ctx.fused:
             grad_X, grad_W = mxfp8_backward_unfused(ctx, grad_Y, X, W)
+            grad_b = grad_Y.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
         else:
-            grad_X, grad_W = mxfp8_backward(ctx, grad_Y, W, X, None, None)
-        grad_b = grad_Y.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+            grad_X, grad_W, grad_b = mxfp8_backward(ctx, grad_Y, W, X, None, None)
         return grad_X, grad_W, grad_b, None
 
 

@@ -78,11 +78,13 @@ class Nvfp4Matmul(torch.autograd.Function):
                 _, _, Wtc, Wtsf = F.quant_pair("nvfp4", W, False, True)
             if need_dw and Xtc is None:
                 _, _, Xtc, Xtsf = F.quant_pair("nvfp4", X, False, True)
-            Gc, Gsf, Gtc, Gtsf = F.quant_pair("nvfp4", grad_Y, need_dx, need_dw, sr=True)
+            need_db = ctx.has_bias and ctx.needs_input_grad[2]
+            Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, need_dw, need_db, sr=True)
             if need_dx:
                 grad_X = F.gemm("nvfp4", Gc, Gsf, Wtc, Wtsf, None, grad_Y.dtype)
             if need_dw:
                 grad_W = F.gemm("nvfp4", Gtc, Gtsf, Xtc, Xtsf, None, grad_Y.dtype)
+            return grad_X, grad_W, grad_b, None
         if ctx.has_bias and ctx.needs_input_grad[2]:
             grad_b = grad_Y.sum(dim=0)
         return grad_X, grad_W, grad_b, None

@@ -41,11 +41,13 @@ def _check_2d(tensor, what):
 
 
 # ------------------------------------------------------------------ NVFP4
-def nvfp4_fused(tensor, want_row=True, want_t=False, sr=False, seed=None, noise=None, noise_t=None):
+def nvfp4_fused(tensor, want_row=True, want_t=False, sr=False, seed=None, noise=None, noise_t=None,
+                bias_grad_dtype=None):
     """-> (codes [R, C/2], sf, codes_t [C, R/2], sf_t) as uint8 tensors (None where not requested).
 
     sr=True with explicit noise tensors is the bit-exact parity mode; without them the
-    kernel generates its own uniform noise from `seed`."""
+    kernel generates its own uniform noise from `seed`.  bias_grad_dtype adds a fifth result:
+    the column sums of `tensor` (the bias gradient when `tensor` is dY), taken in the same pass."""
     _check_2d(tensor, "nvfp4")
     if not sr:
         mode = _ops.SR_NONE
@@ -55,7 +57,7 @@ def nvfp4_fused(tensor, want_row=True, want_t=False, sr=False, seed=None, noise=
         mode = _ops.SR_HASH
         if seed is None:
             seed = int(torch.randint(0, 2 ** 62, (1,)).item())
-    return _ops.quantize_nvfp4(tensor, want_row, want_t, mode, noise, noise_t, seed or 0)
+    return _ops.quantize_nvfp4(tensor, want_row, want_t, mode, noise, noise_t, seed or 0, bias_grad_dtype)
 
 
 def quantize_nvfp4(tensor, rowwise=True, simulated=True, stochastic_rounding=False):
@@ -116,10 +118,11 @@ def q_nvfp4_colwise(tensor, sr=False):
 
 
 # ------------------------------------------------------------------ MXFP8
-def mxfp8_fused(tensor, want_row=True, want_t=False):
-    """-> (codes [R, C], sf, codes_t [C, R], sf_t) as uint8 tensors (None where not requested)."""
+def mxfp8_fused(tensor, want_row=True, want_t=False, bias_grad_dtype=None):
+    """-> (codes [R, C], sf, codes_t [C, R], sf_t) as uint8 tensors (None where not requested);
+    with bias_grad_dtype also the column sums of `tensor`."""
     _check_2d(tensor, "mxfp8")
-    return _ops.quantize_mxfp8(tensor, want_row, want_t)
+    return _ops.quantize_mxfp8(tensor, want_row, want_t, bias_grad_dtype)
 
 
 def q_mxfp8_rowwise(tensor):

@@ -110,6 +110,28 @@ FP4T_API int fp4t_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int64
                         fp4t_stream_t stream);
 
 /*
+ * The same quantizers with the bias gradient fused in: while the kernel walks dY for the
+ * transposed operand it also accumulates the column sums of dY, so
+ *   bias_grad[c] = sum_r x[r, c]      (bf16 or fp32, selected by bias_grad_dtype)
+ * comes out of the pass that already reads every element.  colsum_scratch is caller-owned
+ * scratch of cols fp32 values (contents on entry are ignored; it is cleared on the stream,
+ * accumulated into with atomics and read by a small finishing kernel).  The sum is taken in
+ * fp32; its last bits depend on the order of the atomics.
+ *
+ * Replaces `grad_b = grad_Y.sum(dim=0)` at custom/linear/nvfp4.py:88 and
+ * custom/linear/mxfp8.py:83 (a separate full read of dY in the reference).
+ */
+FP4T_API int fp4t_quantize_nvfp4_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                       void* codes, void* sf, void* codes_t, void* sf_t,
+                                       int sr_mode, const float* noise, const float* noise_t, uint64_t seed,
+                                       float* colsum_scratch, void* bias_grad, int bias_grad_dtype,
+                                       fp4t_stream_t stream);
+FP4T_API int fp4t_quantize_mxfp8_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                       void* codes, void* sf, void* codes_t, void* sf_t,
+                                       float* colsum_scratch, void* bias_grad, int bias_grad_dtype,
+                                       fp4t_stream_t stream);
+
+/*
  * Block-scaled GEMMs on tcgen05:  D[rows, cols] = P[rows, K] . Q[cols, K]^T (+ bias[cols]),
  * fp32 accumulation in tensor memory, D written as bf16 or fp32 (row-major,
  * leading dimension ldd elements).  P/Q are code matrices, p_sf/q_sf their

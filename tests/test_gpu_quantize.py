@@ -191,3 +191,29 @@ def test_misc_byte_ops(ops):
     _eq(packed, orc.pack_fp4_pairs(orc.e2m1_encode_rne_sat(vals)), "pack")
     assert torch.equal(ops.unpack_e2m1(packed).cpu(), vals)
     _eq(ops.pack_e2m1(vals.to(torch.bfloat16).cuda()), packed, "pack bf16")
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8"])
+@pytest.mark.parametrize("rows,cols", [(256, 384), (64, 96), (1024, 192), (96, 4096), (50, 64), (32, 40)])
+def test_fused_bias_gradient(ops, fmt, rows, cols):
+    """Column sums taken inside the quantizer pass equal the separate fp32 column sum, and the
+    codes are the same as without the fusion."""
+    if fmt == "mxfp8" and cols % 32:
+        pytest.skip("row-wise MXFP8 needs cols % 32 == 0")
+    if fmt == "nvfp4" and cols % 16:
+        cols = cols // 16 * 16 + 16
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=g) * 1e-2).to(torch.bfloat16).cuda()
+    want_t = rows % 32 == 0
+    q = ops.quantize_nvfp4 if fmt == "nvfp4" else ops.quantize_mxfp8
+    plain = q(x, True, want_t)
+    for dt, tol in ((torch.float32, 1e-6), (torch.bfloat16, 8e-3)):
+        fused = q(x, True, want_t, bias_grad_dtype=dt)
+        for a, b in zip(plain, fused[:4]):
+            assert (a is None and b is None) or torch.equal(a, b)
+        ref = x.float().sum(dim=0)
+        assert fused[4].dtype == dt and fused[4].shape == (cols,)
+        assert torch.allclose(fused[4].float(), ref, rtol=tol, atol=tol * float(ref.abs().max()) + 1e-7)
+    # two calls in a row share the scratch buffer and must not leak into each other
+    again = q(x * 2, True, want_t, bias_grad_dtype=torch.float32)
+    assert torch.allclose(again[4], (x * 2).float().sum(dim=0), rtol=1e-6, atol=1e-6)
