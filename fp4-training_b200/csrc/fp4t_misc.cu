@@ -62,9 +62,11 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void
                          uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer,
                          CUtensorMapSwizzle swizzle) {
   // The encode call goes to the driver directly and needs a current context.  A thread that
-  // has made no runtime call yet (e.g. an autograd worker on device 0) has none bound; any
-  // runtime call binds the primary context of the current device.
-  FP4T_CUDA(cudaFree(nullptr));
+  // has made no runtime call yet (e.g. an autograd worker on device 0) has none bound;
+  // selecting the device it already has binds that device's primary context.
+  int cur_dev = 0;
+  FP4T_CUDA(cudaGetDevice(&cur_dev));
+  FP4T_CUDA(cudaSetDevice(cur_dev));
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from the driver");
