@@ -32,6 +32,9 @@ _SIGNATURES = {
     "fp4t_quantize_nvfp4_bgrad": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
                                                   ctypes.c_int, _c_vp, _c_vp, ctypes.c_uint64, _c_vp, _c_vp, ctypes.c_int,
                                                   _c_vp]),
+    "fp4t_quantize_nvfp4_bgrad_static": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp,
+                                                         _c_vp, ctypes.c_int, _c_vp, _c_vp, ctypes.c_uint64, _c_vp,
+                                                         ctypes.c_int, _c_vp]),
     "fp4t_quantize_mxfp8_bgrad": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
                                                   _c_vp, _c_vp, ctypes.c_int, _c_vp]),
     "fp4t_gemm_nvfp4": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,

@@ -12,6 +12,8 @@
 //
 // A second, generic kernel handles fp32 input and unaligned shapes with plain
 // per-block loops; it is the slow but general form of the same arithmetic.
+#include <mutex>
+
 #include "fp4t_common.cuh"
 #include "fp4t_ptx.cuh"
 
@@ -645,6 +647,51 @@ extern "C" int fp4t_quantize_mxfp8_bgrad(const void* x, int x_dtype, int64_t row
                                          fp4t_stream_t stream) {
   return fp4t::quantize_bgrad<fp4t::kMxfp8>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, FP4T_SR_NONE,
                                             nullptr, nullptr, 0, colsum_scratch, bias_grad, bias_grad_dtype,
+                                            reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of fp4t_quantize_nvfp4_bgrad: the fp32 column-sum scratch lives in
+// this file-scope device array instead of caller memory.  Every GPU that loads the library
+// carries the array (64 KiB) until the process exits.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_static_colsum[FP4T_STATIC_BGRAD_MAX_COLS];
+
+namespace fp4t {
+namespace {
+// In host code `g_static_colsum` is only a handle for the runtime; the address kernels and
+// memsets must be given is looked up once per device, with that device current.
+int static_colsum_address(float** out) {
+  static std::mutex mu;
+  static float* addr[64] = {nullptr};
+  int dev = 0;
+  FP4T_CUDA(cudaGetDevice(&dev));
+  FP4T_REQUIRE(dev >= 0 && dev < 64, "fp4t_quantize_nvfp4_bgrad_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    FP4T_CUDA(cudaGetSymbolAddress(&p, g_static_colsum));
+    addr[dev] = static_cast<float*>(p);
+  }
+  *out = addr[dev];
+  return FP4T_OK;
+}
+}  // namespace
+}  // namespace fp4t
+
+extern "C" int fp4t_quantize_nvfp4_bgrad_static(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                                void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
+                                                const float* noise, const float* noise_t, uint64_t seed,
+                                                void* bias_grad, int bias_grad_dtype, fp4t_stream_t stream) {
+  FP4T_REQUIRE(cols <= FP4T_STATIC_BGRAD_MAX_COLS,
+               "fp4t_quantize_nvfp4_bgrad_static: cols=%lld exceeds the built-in scratch of %d columns; "
+               "use fp4t_quantize_nvfp4_bgrad with caller scratch",
+               (long long)cols, (int)FP4T_STATIC_BGRAD_MAX_COLS);
+  float* scratch = nullptr;
+  const int rc = fp4t::static_colsum_address(&scratch);
+  if (rc != FP4T_OK) return rc;
+  return fp4t::quantize_bgrad<fp4t::kNvfp4>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise,
+                                            noise_t, seed, scratch, bias_grad, bias_grad_dtype,
                                             reinterpret_cast<cudaStream_t>(stream));
 }
 

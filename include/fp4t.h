@@ -132,6 +132,39 @@ FP4T_API int fp4t_quantize_mxfp8_bgrad(const void* x, int x_dtype, int64_t rows,
                                        fp4t_stream_t stream);
 
 /*
+ * fp4t_quantize_nvfp4_bgrad without any caller-provided scratch.  (No counterpart in the
+ * reference: this entry point exists for hosts that may not allocate device memory around the
+ * call.)
+ *
+ * Some callers cannot hand over a scratch buffer because they cannot obtain one: a plugin
+ * whose host framework owns all device memory and gives plugins only their input and output
+ * tensors, a service that reserved the whole GPU for its own pool at start-up so that a
+ * cudaMalloc made later fails or stalls, or a latency-critical loop that must not hit the
+ * device-wide synchronisation an allocation can cause.  For them the column-sum scratch is a
+ * fixed array inside the library: FP4T_STATIC_BGRAD_MAX_COLS fp32 values (64 KiB) that every
+ * GPU using the library keeps until the process ends.  Inputs and outputs are still the
+ * caller's.  The call itself performs no cudaMalloc / cudaFree and uses no allocating library
+ * routine.
+ *
+ *  - cols larger than FP4T_STATIC_BGRAD_MAX_COLS is rejected with FP4T_ERR_ARG.
+ *  - The first call on each device looks up the array's device address (a one-time host-side
+ *    set-up, done with that device current); make that first call before starting any stream
+ *    capture on the device.
+ *  - All calls on a device share the one array, and it still holds the previous call's sums
+ *    when a call begins; each call clears the columns it uses on its stream before
+ *    accumulating.  Two calls that may run on the GPU at the same time (different streams
+ *    without an ordering between them) would race on it: serialise them.
+ * Results are those of fp4t_quantize_nvfp4_bgrad (identical codes and scales; the bias
+ * gradient differs only by fp32 summation order).
+ */
+#define FP4T_STATIC_BGRAD_MAX_COLS 16384
+FP4T_API int fp4t_quantize_nvfp4_bgrad_static(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                                              int64_t ld, void* codes, void* sf, void* codes_t, void* sf_t,
+                                              int sr_mode, const float* noise, const float* noise_t,
+                                              uint64_t seed, void* bias_grad, int bias_grad_dtype,
+                                              fp4t_stream_t stream);
+
+/*
  * Block-scaled GEMMs on tcgen05:  D[rows, cols] = P[rows, K] . Q[cols, K]^T (+ bias[cols]),
  * fp32 accumulation in tensor memory, D written as bf16 or fp32 (row-major,
  * leading dimension ldd elements).  P/Q are code matrices, p_sf/q_sf their
