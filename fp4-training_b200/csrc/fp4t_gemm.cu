@@ -32,7 +32,6 @@
 // caller's status word, stops issuing work, lets copies in flight land and releases its
 // tensor memory before returning.
 #include <cuda.h>
-#include <cstdio>
 #include <cstdlib>
 
 #include "fp4t_common.cuh"
@@ -44,9 +43,7 @@ namespace {
 enum { kNvfp4 = 0, kMxfp8 = 1 };
 
 constexpr int kBM = 128;             // rows of P per tile (the MMA M)
-constexpr int kGemmThreads = 256;
 constexpr int kTmemCols = 512;
-constexpr int kSfTmemBase = 464;     // scale factors live in the last 48 columns
 
 constexpr int kGemm1Threads = 384;
 
@@ -97,9 +94,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
-}
 template <int kFmt>
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                        uint32_t accumulate, uint32_t sfa, uint32_t sfb) {
@@ -135,7 +129,6 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 // [32,46) stride byte offset>>4, [46,48) version = 1, [61,64) swizzle mode.  The low word is
 // just (shared address >> 4), so stepping through a stage is one 32-bit add.
 constexpr uint32_t kDescHiOperand = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8-row groups 1024 B apart, 128-byte swizzle
-constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                      // 8-row groups 128 B apart, no swizzle
 __device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
   uint64_t d;
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
@@ -486,8 +479,12 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 // memory (the MMA reads both halves across the pair), so the Q-operand traffic per SM is
 // halved compared with the one-CTA kernel; the accumulator of each CTA is 128 lanes x kBN
 // columns in its own tensor memory.  Every load is a plain tiled TMA load (no multicast);
-// both CTAs' loads signal the leader CTA's "full" barrier, the leader issues the scale copies
-// and MMAs for the pair and commits to the barriers of both CTAs.
+// both CTAs' operand loads complete on the leader CTA's "full" barrier (armed by the leader
+// alone with the bytes of both), each CTA's scale warps fill their own tensor memory and
+// arrive on the leader's "scales ready" barrier, and the leader issues the MMAs for the pair
+// and commits to the barriers of both CTAs.  Remote arrives are the plain form (no
+// cluster-scope release): an arrive with .release.cluster from the second CTA every stage
+// cost about 1 us per stage.
 // ------------------------------------------------------------------------------------
 constexpr int kGemm2Threads = 384;
 
@@ -528,12 +525,6 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// arrive (+ expected bytes) on an mbarrier that may live in the other CTA of the cluster
-__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
-               "r"(bytes)
-               : "memory");
-}
 // Arrive on an mbarrier of either CTA of the pair.  What is handed over lives in tensor memory
 // (ordered by the tcgen05 fences), so no cluster-scope release of ordinary memory is requested.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
@@ -549,9 +540,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
 __device__ __forceinline__ void tc2_commit(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
-}
-__device__ __forceinline__ void tc2_cp_sf(uint32_t tmem_addr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
 }
 template <int kFmt>
 __device__ __forceinline__ void tc2_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -906,7 +894,6 @@ int launch_gemm2(const void* p_codes, const void* q_codes, const GemmParams& g0,
   if (rc != FP4T_OK) return rc;
   const int pair_tiles = ((g.m_tiles + 1) / 2) * g.n_tiles;
   const int nclusters = pair_tiles < clusters ? pair_tiles : clusters;
-  if (getenv("FP4T_VERBOSE")) fprintf(stderr, "[fp4t] gemm2 fmt=%d BN=%d clusters=%d (max %d) pair_tiles=%d stages=%d\n", kFmt, kBN, nclusters, clusters, pair_tiles, C::kStages);
   auto kern = gemm2_blockscaled_kernel<kFmt, kBN>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * nclusters, 1, 1);

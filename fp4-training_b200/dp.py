@@ -1,0 +1,97 @@
+"""Data-parallel gradient exchange for the quantized-linear training step.
+
+The reference trains on one GPU (`main_train_tinyvit_mnist.py:31`); running its step data
+parallel adds exactly one exchange: the all-reduce (average) of the parameter gradients the
+wgrad GEMMs produce.  `GradAllReducer` does that exchange with `torch.distributed` (NCCL over
+NVLink on GPUs, gloo on CPU for tests): parameters are grouped into buckets in reverse
+registration order (the order backward produces their gradients), a bucket's all-reduce is
+launched asynchronously as soon as its last gradient has been accumulated, so the reduction of
+late layers overlaps the backward pass of earlier ones, and `finish()` waits for all buckets
+and writes the averaged gradients back.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+class _Bucket:
+    def __init__(self, params):
+        self.params = params
+        p0 = params[0]
+        self.flat = torch.zeros(sum(p.numel() for p in params), dtype=p0.dtype, device=p0.device)
+        self.views = []
+        off = 0
+        for p in params:
+            self.views.append(self.flat[off:off + p.numel()].view_as(p))
+            off += p.numel()
+        self.pending = len(params)
+        self.work = None
+
+
+class GradAllReducer:
+    def __init__(self, params, process_group=None, bucket_bytes: int = 4 << 20):
+        self.group = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        params = [p for p in params if p.requires_grad]
+        self.buckets = []
+        cur, cur_bytes, key = [], 0, None
+        for p in reversed(params):
+            k = (p.dtype, p.device)
+            if cur and (k != key or cur_bytes + p.numel() * p.element_size() > bucket_bytes):
+                self.buckets.append(_Bucket(cur))
+                cur, cur_bytes = [], 0
+            cur.append(p)
+            cur_bytes += p.numel() * p.element_size()
+            key = k
+        if cur:
+            self.buckets.append(_Bucket(cur))
+        self._index = {}
+        self._handles = []
+        for b in self.buckets:
+            for i, p in enumerate(b.params):
+                self._index[p] = (b, i)
+                self._handles.append(p.register_post_accumulate_grad_hook(self._on_grad))
+
+    def _on_grad(self, p):
+        if self.world == 1:
+            return
+        b, i = self._index[p]
+        b.views[i].copy_(p.grad)
+        b.pending -= 1
+        if b.pending == 0:
+            b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
+
+    def finish(self):
+        """Wait for every bucket and store the averaged gradients in `.grad`."""
+        if self.world == 1:
+            return
+        for b in self.buckets:
+            if b.pending != 0:
+                # a parameter received no gradient this step: reduce what there is
+                for i, p in enumerate(b.params):
+                    if p.grad is None:
+                        b.views[i].zero_()
+                b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
+            b.work.wait()
+            b.flat.div_(self.world)
+            for v, p in zip(b.views, b.params):
+                if p.grad is None:
+                    p.grad = v.clone()
+                else:
+                    p.grad.copy_(v)
+            b.pending = len(b.params)
+            b.work = None
+
+    def remove(self):
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+
+
+def broadcast_parameters(module: torch.nn.Module, src: int = 0, process_group=None):
+    """Make every rank start from rank `src`'s parameters and buffers."""
+    if not dist.is_initialized() or dist.get_world_size(process_group) == 1:
+        return
+    for t in list(module.parameters()) + list(module.buffers()):
+        dist.broadcast(t.data, src=src, group=process_group)

@@ -1,0 +1,105 @@
+"""Data-parallel gradient exchange on CPU ranks (gloo, world size 2): the averaged gradients
+equal the gradients of the same model over the concatenated batch, and a rank that never joins
+makes the others fail with an error instead of hanging."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+from torch import nn
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "fp4-training_b200"))
+    from dp import GradAllReducer, broadcast_parameters
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.manual_seed(100 + rank)                      # different initial weights per rank ...
+    model = nn.Sequential(nn.Linear(16, 32), nn.GELU(), nn.Linear(32, 8))
+    broadcast_parameters(model)                        # ... made equal to rank 0's here
+    reducer = GradAllReducer(model.parameters(), bucket_bytes=1024)   # several buckets
+    assert len(reducer.buckets) > 1
+    g = torch.Generator().manual_seed(5)
+    x_all, y_all = torch.randn(8, 16, generator=g), torch.randn(8, 8, generator=g)
+    xs, ys = x_all[rank * 4:(rank + 1) * 4], y_all[rank * 4:(rank + 1) * 4]
+    out = []
+    for _ in range(2):                                  # two steps: buckets are reusable
+        model.zero_grad(set_to_none=True)
+        nn.functional.mse_loss(model(xs), ys).backward()
+        reducer.finish()
+        out.append([p.grad.clone() for p in model.parameters()])
+    q.put((rank, [p.detach().clone() for p in model.parameters()], out[-1]))
+    dist.destroy_process_group()
+
+
+def test_two_rank_gradient_average_matches_full_batch():
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted([q.get(timeout=120) for _ in procs], key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    (_, w0, g0), (_, w1, g1) = results
+    for a, b in zip(w0, w1):
+        assert torch.equal(a, b)
+    for a, b in zip(g0, g1):
+        assert torch.allclose(a, b, atol=1e-7)
+    # reference: one process, full batch (mean over 8 samples = average of the two 4-sample means)
+    model = nn.Sequential(nn.Linear(16, 32), nn.GELU(), nn.Linear(32, 8))
+    with torch.no_grad():
+        for p, w in zip(model.parameters(), w0):
+            p.copy_(w)
+    g = torch.Generator().manual_seed(5)
+    x_all, y_all = torch.randn(8, 16, generator=g), torch.randn(8, 8, generator=g)
+    nn.functional.mse_loss(model(x_all), y_all).backward()
+    for p, got in zip(model.parameters(), g0):
+        assert torch.allclose(p.grad, got, atol=1e-6)
+
+
+def _lonely_worker(port, q):
+    """Rank 0 of a 2-rank job whose rank 1 never starts."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK="0", WORLD_SIZE="2")
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=3))
+        q.put("joined")
+    except Exception as e:  # noqa: BLE001
+        q.put("error: " + type(e).__name__)
+
+
+def test_missing_rank_is_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(_free_port(), q))
+    p.start()
+    msg = q.get(timeout=90)
+    p.join(timeout=30)
+    assert msg.startswith("error")
+
+
+def test_single_process_is_a_no_op():
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "fp4-training_b200"))
+    from dp import GradAllReducer
+    m = nn.Linear(4, 4)
+    r = GradAllReducer(m.parameters())
+    m(torch.randn(2, 4)).sum().backward()
+    g = m.weight.grad.clone()
+    r.finish()
+    assert torch.equal(g, m.weight.grad)
+    r.remove()
