@@ -16,7 +16,11 @@ from ._lib import SR_HASH, SR_NOISE, SR_NONE  # noqa: F401  (re-exported)
 NVFP4_BLOCK = 16
 MXFP8_BLOCK = 32
 
+import contextlib
+import threading
+
 _status = {}
+_tls = threading.local()
 LAUNCHES = {"quantize": 0, "gemm": 0, "misc": 0}   # kernels enqueued by this process
 
 
@@ -33,6 +37,21 @@ def status_word(device) -> torch.Tensor:
     if key not in _status:
         _status[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _status[key]
+
+
+def _on_device(dev):
+    """Context that makes `dev` current; free when it already is (the common case)."""
+    if dev.index is None or dev.index == torch.cuda.current_device():
+        return contextlib.nullcontext()
+    return torch.cuda.device(dev)
+
+
+def _bind_status(dev):
+    """Point this host thread's status reporting at the device's status word (once per thread/device)."""
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if getattr(_tls, "status_dev", None) != key:
+        _lib.lib().fp4t_set_status_word(_lib.ptr(status_word(dev)))
+        _tls.status_dev = key
 
 
 def check_status(device="cuda") -> None:
@@ -80,7 +99,7 @@ def _quantize(fmt, x, want_row, want_t, sr, noise, noise_t, seed, bias_grad_dtyp
         raise ValueError(f"transposed {fmt} quantization needs rows to be a multiple of 32")
     dev = x.device
     codes = sf = codes_t = sf_t = bgrad = None
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if bias_grad_dtype is not None:
             bgrad = torch.empty(cols, dtype=bias_grad_dtype, device=dev)
         if want_row:
@@ -93,7 +112,7 @@ def _quantize(fmt, x, want_row, want_t, sr, noise, noise_t, seed, bias_grad_dtyp
                 return codes, sf, codes_t, sf_t, bgrad
             return codes, sf, codes_t, sf_t
         L = _lib.lib()
-        L.fp4t_set_status_word(_lib.ptr(status_word(dev)))
+        _bind_status(dev)
         if fmt == "nvfp4":
             if noise is not None:
                 noise = noise.to(torch.float32).reshape(rows, cols).contiguous()
@@ -152,7 +171,7 @@ def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None):
         if bias.ndim != 1 or bias.shape[0] != cols:
             raise RuntimeError(f"bias is expected to be 1D of length {cols}, but got shape {tuple(bias.shape)}")
         bias = bias.to(torch.bfloat16).contiguous()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if out is None:
             out = torch.empty((rows, cols), dtype=out_dtype, device=dev)
         if rows == 0 or cols == 0:

@@ -35,6 +35,22 @@ E4M3_NORM_MAX = 448.0
 E4M3_SUBNORM_MIN = 2 ** -9
 
 
+_seed_state = {"base": None, "count": 0}
+
+
+def _next_seed() -> int:
+    """Seed of the next in-kernel noise stream: torch's initial seed mixed with a call counter
+    (splitmix64), so `torch.manual_seed` makes runs repeatable without a device round trip."""
+    base = torch.initial_seed()
+    if _seed_state["base"] != base:
+        _seed_state["base"], _seed_state["count"] = base, 0
+    _seed_state["count"] += 1
+    z = (base + 0x9E3779B97F4A7C15 * _seed_state["count"]) & (2 ** 64 - 1)
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & (2 ** 64 - 1)
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & (2 ** 64 - 1)
+    return z ^ (z >> 31)
+
+
 def _check_2d(tensor, what):
     if tensor.ndim != 2:
         raise ValueError(f"Input tensor must be 2D for {what} quantization")
@@ -56,7 +72,7 @@ def nvfp4_fused(tensor, want_row=True, want_t=False, sr=False, seed=None, noise=
     else:
         mode = _ops.SR_HASH
         if seed is None:
-            seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+            seed = _next_seed()
     return _ops.quantize_nvfp4(tensor, want_row, want_t, mode, noise, noise_t, seed or 0, bias_grad_dtype)
 
 
