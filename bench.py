@@ -45,8 +45,8 @@ FP4_NOMINAL_TFLOPS = 9000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised
 # under profiles/ (fprop GEMM; quantizer of X).  Both working sets fit the 126 MB L2, so part
 # of the written data had not reached DRAM when the kernel ended.
-GEMM_DRAM_TRAFFIC = {"bytes": 43.7e6, "launch": "fprop 8192x4096x4096", "algorithmic_bytes": 94.4e6 / 3 + 67.1e6}
-QUANT_DRAM_TRAFFIC = {"bytes": 71.4e6, "launch": "X 8192x4096 row+transposed", "algorithmic_bytes": 3.125 * N * IC}
+GEMM_DRAM_TRAFFIC = {"bytes": 42.6e6, "launch": "fprop 8192x4096x4096", "algorithmic_bytes": 94.4e6 / 3 + 67.1e6}
+QUANT_DRAM_TRAFFIC = {"bytes": 71.7e6, "launch": "X 8192x4096 row+transposed", "algorithmic_bytes": 3.125 * N * IC}
 METRIC = "nvfp4_linear_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 WORKLOAD = "nvfp4_linear_fwd_bwd N=8192 IC=OC=4096 bf16 (quantize x3 + fprop/dgrad/wgrad)"
@@ -280,7 +280,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "parallelism": f"dp{world}" if world > 1 else "single",
                    "bias_grad": "fused into the dY quantizer (fp32 atomics + finishing kernel)",
                    "frac_of_nominal_fp4_peak": value / world / FP4_NOMINAL_TFLOPS},
-        "roofline": {"bound": "tensor", "kernel": "gemm_blockscaled_kernel<nvfp4> (fprop+dgrad+wgrad)",
+        "roofline": {"bound": "tensor", "kernel": "gemm2_blockscaled_kernel<nvfp4, 256> two-CTA (fprop+dgrad+wgrad)",
                      "achieved": gemm_tflops, "peak": fp4_peak, "unit": UNIT, "frac": gemm_tflops / fp4_peak,
                      "peak_basis": f"4 x {peaks['source']} sustained bf16 cuBLAS TFLOP/s (FP4:BF16 dense ratio); "
                                    f"nominal dense FP4 is {FP4_NOMINAL_TFLOPS:.0f}",
