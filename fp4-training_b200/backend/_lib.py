@@ -41,6 +41,14 @@ _SIGNATURES = {
                                         _c_i64, _c_vp, _c_vp]),
     "fp4t_gemm_mxfp8": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,
                                         _c_i64, _c_vp, _c_vp]),
+    "fp4t_linear_workspace_bytes": (_c_i64, [ctypes.c_int, _c_i64, _c_i64, _c_i64]),
+    "fp4t_linear_backward_workspace_bytes": (_c_i64, [ctypes.c_int, _c_i64, _c_i64]),
+    "fp4t_linear_forward": (ctypes.c_int, [ctypes.c_int, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, ctypes.c_int,
+                                            _c_i64, _c_i64, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_vp, ctypes.c_int, _c_vp,
+                                            _c_vp]),
+    "fp4t_linear_backward": (ctypes.c_int, [ctypes.c_int, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp,
+                                             _c_vp, _c_i64, _c_vp, _c_i64, _c_vp, ctypes.c_int, ctypes.c_int, _c_vp, _c_vp,
+                                             ctypes.c_uint64, _c_vp, _c_vp]),
     "fp4t_pack_e2m1": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_vp, _c_i64, _c_i64, _c_vp]),
     "fp4t_unpack_e2m1": (ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i64, _c_vp]),
     "fp4t_swizzle_rowwise": (ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i64, _c_vp]),
@@ -83,11 +91,14 @@ def check(rc: int, what: str):
 
 
 def ptr(t):
-    return None if t is None else ctypes.c_void_p(t.data_ptr())
+    """Device address of a tensor as a plain int (ctypes converts it for c_void_p parameters)."""
+    return None if t is None else t.data_ptr()
 
 
 def stream_ptr(device):
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    """Raw handle of torch's current stream on `device`."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(idx)
 
 
 def dtype_code(dt: torch.dtype) -> int:

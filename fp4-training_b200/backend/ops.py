@@ -266,3 +266,58 @@ def transpose_bytes(src: torch.Tensor) -> torch.Tensor:
         _lib.check(rc, "fp4t_transpose_bytes")
         LAUNCHES["misc"] += 1
     return out
+
+
+_FMT = {"nvfp4": 0, "mxfp8": 1}
+
+
+def linear_forward(fmt, x, w, bias, keep_wt, keep_xt, out_dtype):
+    """One C call: quantize W and X (plus the transposed operands asked for) and compute
+    Y = X W^T + bias.  -> (Y, workspace); the workspace feeds linear_backward."""
+    _need_cuda(x, w, bias)
+    n, ic = x.shape
+    oc = w.shape[0]
+    dev = x.device
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    with _on_device(dev):
+        L = _lib.lib()
+        _bind_status(dev)
+        ws = torch.empty(L.fp4t_linear_workspace_bytes(_FMT[fmt], n, ic, oc), dtype=torch.uint8, device=dev)
+        y = torch.empty((n, oc), dtype=out_dtype, device=dev)
+        rc = L.fp4t_linear_forward(_FMT[fmt], x.data_ptr(), _lib.dtype_code(x.dtype), n, ic, x.stride(0),
+                                   w.data_ptr(), _lib.dtype_code(w.dtype), oc, w.stride(0), _lib.ptr(bias),
+                                   y.data_ptr(), _lib.dtype_code(out_dtype), oc, ws.data_ptr(),
+                                   (1 if keep_wt else 0) | (2 if keep_xt else 0), status_word(dev).data_ptr(),
+                                   _lib.stream_ptr(dev))
+        _lib.check(rc, "fp4t_linear_forward")
+        LAUNCHES["quantize"] += 2
+        LAUNCHES["gemm"] += 1
+    return y, ws
+
+
+def linear_backward(fmt, g, ws, ic, need_dx, need_dw, need_db, sr=SR_NONE, noise=None, noise_t=None, seed=0):
+    """One C call: quantize dY once and compute dX, dW and the bias gradient (those asked for)."""
+    _need_cuda(g, ws)
+    n, oc = g.shape
+    dev = g.device
+    with _on_device(dev):
+        L = _lib.lib()
+        _bind_status(dev)
+        bws = torch.empty(L.fp4t_linear_backward_workspace_bytes(_FMT[fmt], n, oc), dtype=torch.uint8, device=dev)
+        dx = torch.empty((n, ic), dtype=g.dtype, device=dev) if need_dx else None
+        dw = torch.empty((oc, ic), dtype=g.dtype, device=dev) if need_dw else None
+        db = torch.empty((oc,), dtype=g.dtype, device=dev) if need_db else None
+        if noise is not None:
+            noise = noise.to(torch.float32).reshape(n, oc).contiguous()
+        if noise_t is not None:
+            noise_t = noise_t.to(torch.float32).reshape(oc, n).contiguous()
+        rc = L.fp4t_linear_backward(_FMT[fmt], g.data_ptr(), _lib.dtype_code(g.dtype), n, oc, g.stride(0), ic,
+                                    ws.data_ptr(), bws.data_ptr(), _lib.ptr(dx), ic, _lib.ptr(dw), ic, _lib.ptr(db),
+                                    _lib.dtype_code(g.dtype), int(sr), _lib.ptr(noise), _lib.ptr(noise_t),
+                                    ctypes.c_uint64(seed & (2 ** 64 - 1)), status_word(dev).data_ptr(),
+                                    _lib.stream_ptr(dev))
+        _lib.check(rc, "fp4t_linear_backward")
+        LAUNCHES["quantize"] += 2 if need_db else 1
+        LAUNCHES["gemm"] += int(need_dx) + int(need_dw)
+    return dx, dw, db

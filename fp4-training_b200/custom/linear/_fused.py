@@ -72,3 +72,36 @@ def gemm(fmt, p, p_sf, q, q_sf, bias, out_dtype):
 
 def can_transpose(t) -> bool:
     return t.shape[0] % 32 == 0
+
+
+def layer_call_ok(fmt, X, W, need_dx, need_dw) -> bool:
+    """Shapes the one-call layer entry points take: every GEMM's K a multiple of 32 and the
+    transposed operands constructible."""
+    n, ic = X.shape
+    oc = W.shape[0]
+    if X.dtype not in (torch.bfloat16, torch.float32) or W.dtype != X.dtype:
+        return False
+    if ic % 32 or n == 0:
+        return False
+    if need_dx and oc % 32:
+        return False
+    if need_dw and n % 32:
+        return False
+    return X.stride(1) == 1 and W.stride(1) == 1
+
+
+def layer_forward(fmt, X, W, b, need_dx, need_dw):
+    return _ops.linear_forward(fmt, X, W, b, need_dx, need_dw, X.dtype)
+
+
+def layer_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db, sr):
+    if not (need_dx or need_dw):
+        return None, None, (grad_Y.sum(dim=0) if need_db else None)
+    if fmt == "nvfp4" and sr:
+        if parity_mode():
+            n, oc = grad_Y.shape
+            noise = torch.rand(n, oc // 16, 16, device=grad_Y.device) if need_dx else None
+            noise_t = torch.rand(oc, n // 16, 16, device=grad_Y.device) if need_dw else None
+            return _ops.linear_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db, _ops.SR_NOISE, noise, noise_t)
+        return _ops.linear_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db, _ops.SR_HASH, seed=Q._next_seed())
+    return _ops.linear_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db)

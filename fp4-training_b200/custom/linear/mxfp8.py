@@ -78,6 +78,12 @@ class Mxfp8MatMul(torch.autograd.Function):
             raise ValueError("Input tensor must be 2D for mxfp8 quantization")
         X = X.contiguous()
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        ctx.layer_call = F.layer_call_ok("mxfp8", X, W, need_dx, need_dw)
+        if ctx.layer_call:
+            Y, ws = F.layer_forward("mxfp8", X, W, b, need_dx, need_dw)
+            ctx.ic = X.shape[1]
+            ctx.save_for_backward(ws)
+            return Y
         Wc, Wsf, Wtc, Wtsf = F.quant_pair("mxfp8", W, True, need_dx and F.can_transpose(W))
         Xc, Xsf, Xtc, Xtsf = F.quant_pair("mxfp8", X, True, need_dw and F.can_transpose(X))
         Y = F.gemm("mxfp8", Xc, Xsf, Wc, Wsf, b, X.dtype)
@@ -94,6 +100,11 @@ class Mxfp8MatMul(torch.autograd.Function):
             X, W = ctx.saved_tensors
             grad_X, grad_W = mxfp8_backward_unfused(ctx, grad_Y, X, W)
             grad_b = grad_Y.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+        elif ctx.layer_call:
+            (ws,) = ctx.saved_tensors
+            need_db = ctx.has_bias and ctx.needs_input_grad[2]
+            grad_X, grad_W, grad_b = F.layer_backward("mxfp8", grad_Y, ws, ctx.ic, ctx.needs_input_grad[0],
+                                                      ctx.needs_input_grad[1], need_db, sr=False)
         else:
             Wtc, Wtsf, Xtc, Xtsf, W, X = ctx.saved_tensors
             grad_X, grad_W, grad_b = mxfp8_backward(ctx, grad_Y, W, X,

@@ -46,6 +46,12 @@ class Nvfp4Matmul(torch.autograd.Function):
             raise ValueError("Input tensor must be 2D for nvfp4 quantization")
         X = X.contiguous()
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        ctx.layer_call = F.layer_call_ok("nvfp4", X, W, need_dx, need_dw)
+        if ctx.layer_call:      # one C call for the layer; the workspace holds the backward operands
+            Y, ws = F.layer_forward("nvfp4", X, W, b, need_dx, need_dw)
+            ctx.ic = X.shape[1]
+            ctx.save_for_backward(ws)
+            return Y
         Wc, Wsf, Wtc, Wtsf = F.quant_pair("nvfp4", W, True, need_dx and F.can_transpose(W))
         Xc, Xsf, Xtc, Xtsf = F.quant_pair("nvfp4", X, True, need_dw and F.can_transpose(X))
         Y = F.gemm("nvfp4", Xc, Xsf, Wc, Wsf, b, X.dtype)
@@ -71,6 +77,12 @@ class Nvfp4Matmul(torch.autograd.Function):
                 Xtq, sXt = ctx.quant['3A'](X.to(grad_Y.dtype).T.contiguous())
                 Gtq, sGt = ctx.quant['3B'](grad_Y.T.contiguous())
                 grad_W, _ = op.cublaslt_mm_nvfp4(TransAB.TN.value, grad_Y.dtype, Xtq, sXt, Gtq, sGt, None)
+        elif ctx.layer_call:
+            (ws,) = ctx.saved_tensors
+            need_db = ctx.has_bias and ctx.needs_input_grad[2]
+            grad_X, grad_W, grad_b = F.layer_backward("nvfp4", grad_Y, ws, ctx.ic, ctx.needs_input_grad[0],
+                                                      ctx.needs_input_grad[1], need_db, sr=True)
+            return grad_X, grad_W, grad_b, None
         else:
             Wtc, Wtsf, Xtc, Xtsf, W, X = ctx.saved_tensors
             need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]

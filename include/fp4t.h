@@ -188,6 +188,36 @@ FP4T_API int fp4t_gemm_mxfp8(const void* p_codes, const void* p_sf, const void* 
                     fp4t_stream_t stream);
 
 /*
+ * A whole linear layer per call.  fmt: 0 = NVFP4, 1 = MXFP8.
+ *
+ * fp4t_linear_forward quantizes W [oc, ic] and X [n, ic] (emitting the transposed operands of
+ * the backward GEMMs as well when `keep` asks for them: bit 0 = W^T for dgrad, bit 1 = X^T for
+ * wgrad) and computes Y [n, oc] = X W^T + bias.  All codes and scales go to `workspace`
+ * (fp4t_linear_workspace_bytes(fmt, n, ic, oc) bytes, 256-byte aligned, caller-owned), which
+ * the caller keeps until the backward call.
+ * fp4t_linear_backward quantizes dY [n, oc] once (stochastic rounding per sr_mode for NVFP4),
+ * and computes any of dX [n, ic] = dY W, dW [oc, ic] = dY^T X and db [oc] = column sums of dY
+ * (null pointers skip an output) from the forward workspace and a second workspace of
+ * fp4t_linear_backward_workspace_bytes(fmt, n, oc) bytes.  Outputs are written in out_dtype.
+ * Shape requirements are those of the quantizer and GEMM entry points (ic, oc multiples of the
+ * block size; n % 32 == 0 for the transposed operands).
+ *
+ * Replaces the bodies of Nvfp4Matmul.forward / .backward (custom/linear/nvfp4.py:25-90) and
+ * Mxfp8MatMul.forward / .backward (custom/linear/mxfp8.py:27-85).
+ */
+FP4T_API int64_t fp4t_linear_workspace_bytes(int fmt, int64_t n, int64_t ic, int64_t oc);
+FP4T_API int64_t fp4t_linear_backward_workspace_bytes(int fmt, int64_t n, int64_t oc);
+FP4T_API int fp4t_linear_forward(int fmt, const void* x, int x_dtype, int64_t n, int64_t ic, int64_t ldx,
+                                 const void* w, int w_dtype, int64_t oc, int64_t ldw, const void* bias_bf16,
+                                 void* y, int y_dtype, int64_t ldy, void* workspace, int keep,
+                                 int32_t* status, fp4t_stream_t stream);
+FP4T_API int fp4t_linear_backward(int fmt, const void* g, int g_dtype, int64_t n, int64_t oc, int64_t ldg,
+                                  int64_t ic, const void* fwd_workspace, void* bwd_workspace,
+                                  void* dx, int64_t lddx, void* dw, int64_t lddw, void* db, int out_dtype,
+                                  int sr_mode, const float* noise, const float* noise_t, uint64_t seed,
+                                  int32_t* status, fp4t_stream_t stream);
+
+/*
  * fp32 values that already lie on the E2M1 grid -> packed codes (RNE, saturate
  * to +-6) and back.  Replaces pack_rowwise_to_2xfp4,
  * custom/backend/csrc/cublaslt_mm_nvfp4.cu:109-182.  in_dtype selects fp32/bf16 input.
