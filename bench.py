@@ -179,6 +179,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    reserve = int(os.environ.get("FP4T_RESERVE_SMS", "0")) if world > 1 else 0
+    if reserve:
+        # optional experiment knob: cap the persistent grids so that some SMs stay free for the
+        # NCCL all-reduce that overlaps the next step's kernels (measured: no gain, default off)
+        from backend import _lib as _l
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        _l.lib().fp4t_set_sm_limit(sms - reserve)
     peaks = measured_peaks()
     nsets = 2   # rotate input sets; one set alone (160 MB bf16) already exceeds the 126 MB L2
     sets = [synth_inputs(N, IC, OC, 100 * rank + s, dev) for s in range(nsets)]
@@ -186,33 +193,28 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         s[1] = sets[0][1]          # weights are shared state, only the batch changes
     bias = sets[0][3]
     ev = torch.cuda.Event
-    # weight / bias gradients land in two rotating buffers so that the NCCL all-reduce of step i
-    # (on a side stream) can overlap the kernels of step i+1, as it does under the backward
-    # pass of the previous layer in data-parallel training
-    dw_bufs = [torch.empty(OC, IC, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    # weight and bias gradients land in one flat buffer (two of them, rotating) so that a single
+    # NCCL all-reduce per step, on a side stream, can overlap the kernels of step i+1, as it
+    # does under the backward pass of the previous layer in data-parallel training
+    grad_bufs = [torch.empty(OC * IC + OC, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     comm_done = [None, None]
 
     def hot_step(i):
         x, w, g, _ = sets[i % nsets]
-        wc, wsf, wtc, wtsf = ops.quantize_nvfp4(w, True, True)
-        xc, xsf, xtc, xtsf = ops.quantize_nvfp4(x, True, True)
-        y = ops.gemm_nvfp4(xc, xsf, wc, wsf, bias, torch.bfloat16)
-        gc, gsf, gtc, gtsf, db = ops.quantize_nvfp4(g, True, True, sr=ops.SR_HASH, seed=i,
-                                                    bias_grad_dtype=torch.bfloat16)
-        dx = ops.gemm_nvfp4(gc, gsf, wtc, wtsf, None, torch.bfloat16)
+        y, ws = ops.linear_forward("nvfp4", x, w, bias, True, True, torch.bfloat16)
         slot = i % 2
         if comm_done[slot] is not None:
             torch.cuda.current_stream().wait_event(comm_done[slot])   # buffer free again
-        dw = ops.gemm_nvfp4(gtc, gtsf, xtc, xtsf, None, torch.bfloat16, out=dw_bufs[slot])
+        flat = grad_bufs[slot]
+        dx, dw, db = ops.linear_backward("nvfp4", g, ws, IC, True, True, True, sr=ops.SR_HASH, seed=i,
+                                         out_dw=flat[:OC * IC].view(OC, IC), out_db=flat[OC * IC:])
         if world > 1:
             ready = ev()
             ready.record()
             with torch.cuda.stream(comm_stream):
                 comm_stream.wait_event(ready)
-                db.record_stream(comm_stream)
-                dist.all_reduce(dw)
-                dist.all_reduce(db)
+                dist.all_reduce(flat)
                 comm_done[slot] = ev()
                 comm_done[slot].record()
         return y, dx, dw, db

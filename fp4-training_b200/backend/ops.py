@@ -296,8 +296,11 @@ def linear_forward(fmt, x, w, bias, keep_wt, keep_xt, out_dtype):
     return y, ws
 
 
-def linear_backward(fmt, g, ws, ic, need_dx, need_dw, need_db, sr=SR_NONE, noise=None, noise_t=None, seed=0):
-    """One C call: quantize dY once and compute dX, dW and the bias gradient (those asked for)."""
+def linear_backward(fmt, g, ws, ic, need_dx, need_dw, need_db, sr=SR_NONE, noise=None, noise_t=None, seed=0,
+                    out_dw=None, out_db=None):
+    """One C call: quantize dY once and compute dX, dW and the bias gradient (those asked for).
+    out_dw [oc, ic] / out_db [oc] (dtype of g, contiguous) receive the results in place, e.g.
+    views of one flat gradient buffer that is all-reduced with a single collective."""
     _need_cuda(g, ws)
     n, oc = g.shape
     dev = g.device
@@ -306,8 +309,8 @@ def linear_backward(fmt, g, ws, ic, need_dx, need_dw, need_db, sr=SR_NONE, noise
         _bind_status(dev)
         bws = torch.empty(L.fp4t_linear_backward_workspace_bytes(_FMT[fmt], n, oc), dtype=torch.uint8, device=dev)
         dx = torch.empty((n, ic), dtype=g.dtype, device=dev) if need_dx else None
-        dw = torch.empty((oc, ic), dtype=g.dtype, device=dev) if need_dw else None
-        db = torch.empty((oc,), dtype=g.dtype, device=dev) if need_db else None
+        dw = (out_dw if out_dw is not None else torch.empty((oc, ic), dtype=g.dtype, device=dev)) if need_dw else None
+        db = (out_db if out_db is not None else torch.empty((oc,), dtype=g.dtype, device=dev)) if need_db else None
         if noise is not None:
             noise = noise.to(torch.float32).reshape(n, oc).contiguous()
         if noise_t is not None:

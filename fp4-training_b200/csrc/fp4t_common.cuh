@@ -32,8 +32,10 @@ int cuda_fail(cudaError_t e, const char* what);
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-// Number of SMs of the current device, or -1 if it is not an sm_100 part.
+// Number of SMs the persistent kernels may fill on the current device (the device's SM count,
+// or the smaller process-wide limit set with fp4t_set_sm_limit), or -1 if it is not an sm_100 part.
 int sm_count();
+int sm_limit();
 
 // 2-D tiled tensor map over a row-major matrix [outer, inner] of `dtype` elements whose rows
 // are row_pitch_bytes apart; out-of-range parts of a box read as zero.

@@ -893,6 +893,8 @@ int launch_gemm2(const void* p_codes, const void* q_codes, const GemmParams& g0,
   rc = make_sf_map(&map_qsf, g.q_sf, g.cols, g.ntx, C::kSfBoxElems);
   if (rc != FP4T_OK) return rc;
   const int pair_tiles = ((g.m_tiles + 1) / 2) * g.n_tiles;
+  const int lim = sm_limit();
+  if (lim > 0 && lim / 2 < clusters) clusters = lim / 2 > 0 ? lim / 2 : 1;
   const int nclusters = pair_tiles < clusters ? pair_tiles : clusters;
   auto kern = gemm2_blockscaled_kernel<kFmt, kBN>;
   cudaLaunchConfig_t cfg = {};

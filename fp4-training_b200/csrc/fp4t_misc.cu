@@ -2,6 +2,7 @@
 // scale-matrix re-layouts and a byte transpose.  All are HBM-bound copies with index
 // arithmetic; they exist for operand forms the reference's op signatures accept and the
 // fused quantizers do not already produce.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -26,6 +27,9 @@ int cuda_fail(cudaError_t e, const char* what) {
 static thread_local int32_t* g_status_word = nullptr;
 int32_t* current_status_word() { return g_status_word; }
 
+static std::atomic<int> g_sm_limit{0};
+int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -36,6 +40,8 @@ int sm_count() {
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     cached[dev] = (major == 10 && n > 0) ? n : -1;
   }
+  const int lim = sm_limit();
+  if (cached[dev] > 0 && lim > 0 && lim < cached[dev]) return lim;
   return cached[dev];
 }
 
@@ -168,6 +174,12 @@ using namespace fp4t;
 
 extern "C" const char* fp4t_last_error(void) { return fp4t::g_error; }
 extern "C" int fp4t_version(void) { return 101; }
+
+extern "C" int fp4t_set_sm_limit(int sms) {
+  FP4T_REQUIRE(sms >= 0, "fp4t_set_sm_limit: negative limit");
+  fp4t::g_sm_limit.store(sms, std::memory_order_relaxed);
+  return FP4T_OK;
+}
 
 extern "C" int fp4t_set_status_word(int32_t* device_word) {
   fp4t::g_status_word = device_word;

@@ -71,6 +71,13 @@ FP4T_API int fp4t_version(void);
  */
 FP4T_API int fp4t_set_status_word(int32_t* device_word);
 
+/*
+ * Process-wide cap on the number of SMs the persistent kernels fill (0 = all).  A data-parallel
+ * job sets it a little below the SM count so that a collective running on another stream finds
+ * free SMs instead of waiting behind a grid that occupies every one.
+ */
+FP4T_API int fp4t_set_sm_limit(int sms);
+
 /* Bytes of the swizzled scale buffer for a logical [outer, kblocks] scale matrix. */
 FP4T_API int64_t fp4t_sf_bytes(int64_t outer, int64_t kblocks);
 
