@@ -83,6 +83,7 @@ struct GemmParams {
   int m_tiles, n_tiles, k_stages;
   int out_f32;
   int vec_ok;       // 16-byte stores allowed
+  int tma_ok;       // the output can be written with tiled TMA stores
   int32_t* status;
 };
 
@@ -203,6 +204,79 @@ __device__ __forceinline__ void store_chunk(const GemmParams& g, const int row, 
       }
     }
   }
+}
+
+
+// Epilogue of one 32-row x 32-column chunk through shared memory and one tiled TMA store.
+// Each lane holds one row of the chunk in registers; the rows go to a swizzled staging tile
+// (conflict-free 16-byte writes) that the TMA store un-swizzles and clips at the matrix
+// edges.  Thread-per-row stores straight to global memory scatter 16-byte pieces over 32
+// rows per instruction and kept the load/store pipe busy for microseconds per tile, which
+// delayed the scale-factor warps and with them the main loop.
+// `buf` is this warp's staging area (4 KB, 1024-byte aligned): two 2-KB tiles for bf16 output
+// that alternate, one 4-KB tile for fp32 output.
+__device__ __forceinline__ void emit_chunk(const GemmParams& g, const CUtensorMap* map_d, uint8_t* buf, uint32_t& n_emit,
+                                           const int lane, const int row0, const int col0, const uint32_t (&r)[32]) {
+  if (row0 >= g.rows || col0 >= g.cols) return;   // warp-uniform
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (g.bias != nullptr) {
+    if (g.vec_ok && col0 + 32 <= g.cols) {
+      const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint4 b = __ldg(bp + q4);
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[q4 * 8 + 2 * j] += __uint_as_float(bw[j] << 16);
+          v[q4 * 8 + 2 * j + 1] += __uint_as_float(bw[j] & 0xFFFF0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < g.cols) v[j] += __bfloat162float(g.bias[col0 + j]);
+    }
+  }
+  if (g.out_f32) {
+    if (lane == 0) bulk_wait_read<0>();
+    __syncwarp();
+    uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float4*>(rowp + ((j ^ (lane & 7)) << 4)) =
+          make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map_d, smem_u32(buf), col0, row0);
+      bulk_commit();
+    }
+  } else {
+    uint8_t* tile = buf + (n_emit & 1u) * 2048;
+    if (lane == 0) bulk_wait_read<1>();
+    __syncwarp();
+    uint8_t* rowp = tile + lane * 64;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+        w[t] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(rowp + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map_d, smem_u32(tile), col0, row0);
+      bulk_commit();
+    }
+  }
+  ++n_emit;
 }
 
 // ------------------------------------------------------------------------------------
@@ -399,6 +473,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
           const uint32_t j = k - C::kSfBufs;
           if (!mbar_wait(bar_empty + 8 * (j % C::kStages), (j / C::kStages) & 1u, abort_flag, g.status, 6)) { ok = false; break; }
         }
+        __syncwarp();   // lanes leave the polling loop at different times; tcgen05.st needs the whole warp
         tc_fence_after();
         const uint32_t sfa_t = tmem_base + lane_sel + C::kSfBuf0 + (k % C::kSfBufs) * C::kSfBufStride;
         const uint32_t sfb_t = sfa_t + C::kSfbOff;
@@ -485,6 +560,12 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 // and commits to the barriers of both CTAs.  Remote arrives are the plain form (no
 // cluster-scope release): an arrive with .release.cluster from the second CTA every stage
 // cost about 1 us per stage.
+//   Warp roles per CTA: 0 operand producer, 1 MMA issuer (leader only), 2 tensor-memory
+// allocation, 3 scale-tile producer, 4-7 epilogue, 8-11 scale factors.  Operands and scale
+// tiles have separate shared-memory rings (a scale slot is free once its bytes sit in the
+// scale warps' registers), and the epilogue leaves through swizzled staging tiles and tiled
+// TMA stores (clipped at the matrix edges); an output whose base or pitch is not 16-byte
+// aligned falls back to per-thread stores.
 // ------------------------------------------------------------------------------------
 constexpr int kGemm2Threads = 384;
 
@@ -496,9 +577,22 @@ struct Cfg2 {
   static constexpr int kBBytes = (kBN / 2) * 128;            // this CTA's half of the Q slab
   static constexpr int kSfaBytes = kSfChunks * 512;
   static constexpr int kSfbBytes = kOuterB * kSfChunks * 512;  // scales of ALL kBN columns
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = (220 * 1024) / kStageBytes > 8 ? 8 : (220 * 1024) / kStageBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+  // Operands and scale tiles live in separate rings.  A scale slot is free again as soon as
+  // the scale warps hold its bytes in registers, long before the MMAs that use the operand
+  // stage complete, so a short scale ring leaves room for one more operand stage: the main
+  // loop is bound by bytes in flight (round trip x bandwidth), not by the tensor pipe.
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSfSlotBytes = kSfaBytes + kSfbBytes;
+  static constexpr int kSfSlots = 3;
+  static constexpr int kEpiBytes = 4 * 4096;                   // staging tiles of the four epilogue warps
+  static constexpr int kBarBytes = 512;
+  // the dynamic shared memory window is declared 1024-byte aligned (checked at run time), so no slack
+  static constexpr int kBudget = 227 * 1024 - kBarBytes - kEpiBytes - kSfSlots * kSfSlotBytes;
+  static constexpr int kStages = kBudget / kStageBytes > 8 ? 8 : kBudget / kStageBytes;
+  static constexpr int kEpi0 = kStages * kStageBytes;          // byte offsets of the regions after the stages
+  static constexpr int kSfRing0 = kEpi0 + kEpiBytes;
+  static constexpr int kBar0 = kSfRing0 + kSfSlots * kSfSlotBytes;
+  static constexpr int kSmemBytes = kBar0 + kBarBytes;
   // tensor memory: accumulators at 0 and kAccStride, two 48-column scale-factor buffers at 416 and 464
   static constexpr int kAccStride = (kBN == 256) ? 160 : 128;
   static constexpr int kChunks = kBN / 32;
@@ -510,6 +604,7 @@ struct Cfg2 {
   static constexpr int kSfBoxElems = kSfChunks * 64;         // 8-byte elements per scale box row
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   static_assert(kAccStride + kBN <= kSfBuf0, "tensor memory budget");
+  static_assert((2 * kStages + 2 * kSfSlots + 4 + 2) * 8 + 8 <= 256, "barrier block (scratch words start at byte 256)");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -563,20 +658,25 @@ template <int kFmt, int kBN>
 __global__ void __launch_bounds__(kGemm2Threads, 1)
 gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_psf, const __grid_constant__ CUtensorMap map_qsf,
-                         const GemmParams g) {
+                         const __grid_constant__ CUtensorMap map_d, const GemmParams g) {
   using C = Cfg2<kFmt, kBN>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_pair[];
+  uint8_t* smem_gen = smem_pair;
+  const uint32_t smem_base = smem_u32(smem_pair);
+  if (smem_base & 1023u) {   // the swizzled tiles need the alignment the declaration asks for
+    if (threadIdx.x == 0 && g.status) atomicCAS(g.status, 0, 29);
+    return;
+  }
 
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kStages * C::kStageBytes);
-  const uint32_t bar_full = smem_u32(bars);                    // [kStages] data of both CTAs landed (leader's copy is used)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kBar0);
+  const uint32_t bar_full = smem_u32(bars);                    // [kStages] operands of both CTAs landed (leader's copy is used)
   const uint32_t bar_empty = bar_full + 8 * C::kStages;        // [kStages] MMAs that read the stage are done
-  const uint32_t bar_sf_land = bar_empty + 8 * C::kStages;     // [kStages] this CTA's own scale tiles landed
-  const uint32_t bar_sf_ready = bar_sf_land + 8 * C::kStages;  // [2] scale factors are in tensor memory (leader's copy)
+  const uint32_t bar_sf_land = bar_empty + 8 * C::kStages;     // [kSfSlots] this CTA's own scale tiles landed
+  const uint32_t bar_sf_free = bar_sf_land + 8 * C::kSfSlots;  // [kSfSlots] the four scale warps hold the slot's bytes
+  const uint32_t bar_sf_ready = bar_sf_free + 8 * C::kSfSlots; // [<=4] scale factors are in tensor memory (leader's copy)
   const uint32_t bar_tmem_full = bar_sf_ready + 32;            // [1]
   const uint32_t bar_tmem_empty = bar_tmem_full + 8;           // [1] (leader's copy is used)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * C::kStages + 6);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 2 * C::kSfSlots + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -590,7 +690,10 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);      // the leader's producer arms it with the bytes of BOTH CTAs
       mbar_init(bar_empty + 8 * s, 1);     // one tcgen05.commit
+    }
+    for (int s = 0; s < C::kSfSlots; ++s) {
       mbar_init(bar_sf_land + 8 * s, 1);
+      mbar_init(bar_sf_free + 8 * s, 4);
     }
     for (int b = 0; b < C::kSfBufs; ++b) mbar_init(bar_sf_ready + 8 * b, 8);   // four scale warps in each CTA
     mbar_init(bar_tmem_full, 1);
@@ -619,35 +722,54 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
 
   if (warp == 0) {
    if (lane == 0) {
-    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    // ------------------------------ operand producer (both CTAs) ------------------------------
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
-      const int m_tile = pm * 2 + (int)rank;                 // this CTA's 128-row tile of P
-      const int row_p = m_tile * kBM;
+      const int row_p = (pm * 2 + (int)rank) * kBM;           // this CTA's 128-row tile of P
       const int row_q = n_idx * kBN + (int)rank * (kBN / 2);  // this CTA's half of the Q rows
       for (int ks = 0; ks < g.k_stages; ++ks) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 21)) { ok = false; break; }
         const uint32_t a_s = smem_base + stage * C::kStageBytes;
         const uint32_t b_s = a_s + C::kABytes;
-        const uint32_t sfa_s = b_s + C::kBBytes;
-        const uint32_t sfb_s = sfa_s + C::kSfaBytes;
         const uint32_t bar = leader_full + 8 * stage;
         // Only the leader arms the barrier, with the bytes both CTAs are about to load; the
         // other CTA's copies simply complete on it (its arrival count keeps the phase open).
-        const uint32_t sbar = bar_sf_land + 8 * stage;
-        mbar_expect_tx(sbar, (uint32_t)(C::kSfaBytes + C::kSfbBytes));
+        if (leader) mbar_expect_tx(bar_full + 8 * stage, 2u * (uint32_t)C::kStageBytes);
+        tma_load_2d_pair(a_s, &map_p, bar, ks * 128, row_p);
+        tma_load_2d_pair(b_s, &map_q, bar, ks * 128, row_q);
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (*abort_flag) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {}
+    }
+   }
+   __syncwarp();
+  } else if (warp == 3) {
+   if (lane == 0) {
+    // ------------------------------ scale-tile producer (both CTAs) ------------------------------
+    int slot = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
+      const int m_tile = pm * 2 + (int)rank;
+      for (int ks = 0; ks < g.k_stages; ++ks) {
+        if (!mbar_wait(bar_sf_free + 8 * slot, phase ^ 1u, abort_flag, g.status, 28)) { ok = false; break; }
+        const uint32_t sfa_s = smem_base + C::kSfRing0 + slot * C::kSfSlotBytes;
+        const uint32_t sfb_s = sfa_s + C::kSfaBytes;
+        const uint32_t sbar = bar_sf_land + 8 * slot;
+        mbar_expect_tx(sbar, (uint32_t)C::kSfSlotBytes);
         tma_load_2d(sfa_s, &map_psf, sbar, ks * C::kSfBoxElems, m_tile);
 #pragma unroll
         for (int o = 0; o < C::kOuterB; ++o) {
           tma_load_2d(sfb_s + o * C::kSfaBytes, &map_qsf, sbar, ks * C::kSfBoxElems, n_idx * C::kOuterB + o);
         }
-        if (leader) mbar_expect_tx(bar_full + 8 * stage, 2u * (uint32_t)(C::kABytes + C::kBBytes));
-        tma_load_2d_pair(a_s, &map_p, bar, ks * 128, row_p);
-        tma_load_2d_pair(b_s, &map_q, bar, ks * 128, row_q);
-        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        if (++slot == C::kSfSlots) { slot = 0; phase ^= 1u; }
       }
     }
     if (*abort_flag) {
@@ -706,13 +828,14 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   } else if (warp >= 8) {
     // ------------------------------ scale-factor warps (both CTAs) ------------------------------
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t sf_scratch = bar_full + 256 + 4 * (warp & 3);   // unused tail of the barrier block
     uint32_t k = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
-        const uint32_t stage = k % C::kStages, use = k / C::kStages;
-        if (!mbar_wait(bar_sf_land + 8 * stage, use & 1u, abort_flag, g.status, 26)) { ok = false; break; }
-        const uint8_t* sfa_s = smem_gen + stage * C::kStageBytes + C::kABytes + C::kBBytes;
+        const uint32_t slot = k % C::kSfSlots, use = k / C::kSfSlots;
+        if (!mbar_wait(bar_sf_land + 8 * slot, use & 1u, abort_flag, g.status, 26)) { ok = false; break; }
+        const uint8_t* sfa_s = smem_gen + C::kSfRing0 + slot * C::kSfSlotBytes;
         const uint8_t* sfb_s = sfa_s + C::kSfaBytes;
         uint32_t va[C::kSfChunks * 4], vb[C::kSfChunks * C::kOuterB * 4];
 #pragma unroll
@@ -726,10 +849,25 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
             vb[j] = u.x; vb[j + 1] = u.y; vb[j + 2] = u.z; vb[j + 3] = u.w;
           }
         }
+        // The slot is handed back before the registers are used, so "the loads have returned" has
+        // to be made explicit: every lane stores a word that depends on each of its loads, and
+        // the arrive (a release, after the warp barrier) cannot pass those stores.  Without this
+        // the refill of the slot raced with loads still in flight.
+        {
+          uint32_t dep = 0;
+#pragma unroll
+          for (int c = 0; c < C::kSfChunks; ++c) dep ^= va[4 * c + 3];
+#pragma unroll
+          for (int j = 0; j < C::kSfChunks * C::kOuterB; ++j) dep ^= vb[4 * j + 3];
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(sf_scratch), "r"(dep) : "memory");
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sf_free + 8 * slot);   // the slot may be refilled
         if (k >= (uint32_t)C::kSfBufs) {   // the MMAs that last read this scale-factor buffer are done
           const uint32_t j = k - C::kSfBufs;
           if (!mbar_wait(bar_empty + 8 * (j % C::kStages), (j / C::kStages) & 1u, abort_flag, g.status, 27)) { ok = false; break; }
         }
+        __syncwarp();   // lanes leave the polling loop at different times; tcgen05.st needs the whole warp
         tc_fence_after();
         const uint32_t sfa_t = tmem_base + lane_sel + C::kSfBuf0 + (k % C::kSfBufs) * C::kSfBufStride;
         const uint32_t sfb_t = sfa_t + C::kSfbOff;
@@ -744,6 +882,8 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   } else if (warp >= 4) {
     // ------------------------------ epilogue (both CTAs) ------------------------------
     const int quad = warp & 3;
+    uint8_t* epi_buf = smem_gen + C::kEpi0 + quad * 4096;
+    uint32_t n_emit = 0;
     int it = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
       const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
@@ -753,10 +893,17 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((it & 1) * C::kAccStride);
-      const int row = (pm * 2 + (int)rank) * kBM + quad * 32 + lane;
+      const int row0 = (pm * 2 + (int)rank) * kBM + quad * 32;
+      const int row = row0 + lane;
       const bool row_ok = row < g.rows;
       const int col_base = n_idx * kBN;
+      auto put = [&](int col0, const uint32_t (&r)[32]) {
+        if (g.tma_ok) emit_chunk(g, &map_d, epi_buf, n_emit, lane, row0, col0, r);
+        else store_chunk(g, row, row_ok, col0, r);
+      };
       if (kBN == 256) {
+        // The columns the other accumulator overlaps go to registers first; then the MMA warp
+        // may start the next tile.
         const int e0 = (it & 1) == 0 ? C::kChunks - C::kEarlyChunks : 0;
         uint32_t early[3][32];
 #pragma unroll
@@ -766,14 +913,14 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);
 #pragma unroll
-        for (int e = 0; e < 3; ++e) store_chunk(g, row, row_ok, col_base + (e0 + e) * 32, early[e]);
+        for (int e = 0; e < 3; ++e) put(col_base + (e0 + e) * 32, early[e]);
         const int r0 = (it & 1) == 0 ? 0 : C::kEarlyChunks;
 #pragma unroll 1
         for (int ci = 0; ci < C::kChunks - C::kEarlyChunks; ++ci) {
           uint32_t r[32];
           tc_ld32(acc + (uint32_t)((r0 + ci) * 32), r);
           tc_wait_ld();
-          store_chunk(g, row, row_ok, col_base + (r0 + ci) * 32, r);
+          put(col_base + (r0 + ci) * 32, r);
         }
       } else {
 #pragma unroll 1
@@ -786,10 +933,12 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);
           }
-          store_chunk(g, row, row_ok, col_base + c * 32, r);
+          put(col_base + c * 32, r);
         }
       }
     }
+    if (lane == 0) bulk_wait_all<0>();   // staged tiles are read and written out before shared memory goes away
+    __syncwarp();
   }
 
   // ------------------------------ teardown ------------------------------
@@ -892,6 +1041,13 @@ int launch_gemm2(const void* p_codes, const void* q_codes, const GemmParams& g0,
   if (rc != FP4T_OK) return rc;
   rc = make_sf_map(&map_qsf, g.q_sf, g.cols, g.ntx, C::kSfBoxElems);
   if (rc != FP4T_OK) return rc;
+  CUtensorMap map_d = {};
+  if (g.tma_ok) {   // 32 x 32 element boxes; the swizzle width equals the box row (64 B bf16, 128 B fp32)
+    rc = encode_tensor_map_2d(&map_d, g.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                              g.d, (uint64_t)g.cols, (uint64_t)g.rows, (uint64_t)g.ldd * (g.out_f32 ? 4 : 2), 32u, 32u,
+                              g.out_f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc != FP4T_OK) return rc;
+  }
   const int pair_tiles = ((g.m_tiles + 1) / 2) * g.n_tiles;
   const int lim = sm_limit();
   if (lim > 0 && lim / 2 < clusters) clusters = lim / 2 > 0 ? lim / 2 : 1;
@@ -909,7 +1065,7 @@ int launch_gemm2(const void* p_codes, const void* q_codes, const GemmParams& g0,
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  FP4T_CUDA(cudaLaunchKernelEx(&cfg, kern, map_p, map_q, map_psf, map_qsf, g));
+  FP4T_CUDA(cudaLaunchKernelEx(&cfg, kern, map_p, map_q, map_psf, map_qsf, map_d, g));
   return FP4T_OK;
 }
 
@@ -954,6 +1110,7 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
   const int esz = g.out_f32 ? 4 : 2;
   g.vec_ok = (reinterpret_cast<uintptr_t>(d) % 16 == 0) && ((ldd * esz) % 16 == 0) &&
              (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
+  g.tma_ok = (reinterpret_cast<uintptr_t>(d) % 16 == 0) && ((ldd * esz) % 16 == 0);
   g.status = status;
   g.n_tiles = 0;
 

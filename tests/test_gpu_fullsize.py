@@ -130,3 +130,25 @@ def test_gemm_sweep_shapes(ops, fmt, m, n, k):
         out = ops.gemm_mxfp8(ac, asf, bc, bsf, None, torch.bfloat16)
     assert orc.rel_frobenius(out.float(), ad @ bd.t()) <= 1e-2
     ops.check_status()
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8"])
+@pytest.mark.parametrize("m,n,k,dtype", [(4096, 4096, 8192, torch.float32), (8192, 4096, 4096, torch.bfloat16),
+                                         (8192, 4096, 4096, torch.float32), (2048, 1536, 4096, torch.bfloat16)])
+def test_gemm_is_deterministic(ops, fmt, m, n, k, dtype):
+    """The GEMM has a fixed accumulation order, so repeated launches on the same operands must
+    agree bit for bit.  A hand-over between the kernel's roles that is not properly ordered (a
+    ring slot refilled while it is still being read, a scale buffer overwritten early) shows up
+    here as a few rows that differ by one K slab's contribution, far below the parity tolerance."""
+    gen = torch.Generator(device="cuda").manual_seed(m + k)
+    a = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", generator=gen).to(torch.bfloat16)
+    quant = ops.quantize_nvfp4 if fmt == "nvfp4" else ops.quantize_mxfp8
+    gemm = ops.gemm_nvfp4 if fmt == "nvfp4" else ops.gemm_mxfp8
+    ac, asf, _, _ = quant(a, True, False)
+    bc, bsf, _, _ = quant(b, True, False)
+    first = gemm(ac, asf, bc, bsf, None, dtype).clone()
+    for _ in range(20):
+        again = gemm(ac, asf, bc, bsf, None, dtype)
+        assert torch.equal(again, first)
+    ops.check_status()
