@@ -123,15 +123,16 @@ constexpr ScaleTable make_scale_table() {
 }
 __device__ __forceinline__ void nvfp4_scale_from_table(const float2* __restrict__ tab, float amax, float& s,
                                                        float& r) {
-  const uint32_t b = __float_as_uint(amax);
+  // amax below 2^-102 would underflow the exponent arithmetic; it ends at the lower clamp anyway
+  const uint32_t b = max(__float_as_uint(amax), 0x0C800000u);
   const float2 t = tab[(b >> 16) & 0x7Fu];
   const uint32_t e = (b & 0x7F800000u) - 0x3F800000u;
   const float sf = __uint_as_float(__float_as_uint(t.x) + e);
   const float rf = __uint_as_float(__float_as_uint(t.y) - e);
-  const bool lo = (b < 0x0C800000u) || (sf < 0x1p-9f);
-  const bool hi = sf > 448.0f;
-  s = lo ? 0x1p-9f : (hi ? 448.0f : sf);
-  r = lo ? 512.0f : (hi ? (1.0f / 448.0f) : rf);
+  // clamp(s, 2^-9, 448); the reciprocal is monotonic, so clamping it to [RN(1/448), 512] gives
+  // RN(1/s) of the clamped scale
+  s = fminf(fmaxf(sf, 0x1p-9f), 448.0f);
+  r = fminf(fmaxf(rf, 1.0f / 448.0f), 512.0f);
 }
 // UE4M3 byte of a scale in [2^-9, 448], round to nearest even, integer / FMA pipes only.
 __device__ __forceinline__ uint32_t e4m3_byte_of_scale(float s) {

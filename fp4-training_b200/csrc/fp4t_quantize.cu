@@ -45,7 +45,7 @@ enum { kNvfp4 = 0, kMxfp8 = 1 };
 // Persistent CTAs (two per SM).  Warp 8 is the producer: it streams 128x128 bf16 tiles into
 // a 3-deep shared-memory ring with TMA (out-of-range parts read as zero).  Warps 0-7 wait on
 // the tile's mbarrier and make two passes over it:
-//   row pass   lane pairs (NVFP4) / quads (MXFP8) own one block of a row; amax by shuffle;
+//   row pass   each thread owns one whole block of a row (two or four 16-byte loads);
 //   column pass each thread owns two adjacent columns and 32 rows, i.e. whole blocks of the
 //              transposed tensor, read from shared memory as packed bf16 pairs.
 // Division by the block scale is done on packed fp32 pairs (reciprocal multiply + one FMA
@@ -102,66 +102,89 @@ struct TileCtx {
   int tid;
 };
 
-// ---- row-wise pass: a thread handles 8 consecutive elements of a row, 8 times ----------
+// ---- row-wise pass: a thread owns one whole block of a row (16 or 32 elements) ----------
+// 8 (NVFP4) or 4 (MXFP8) threads cover a tile row, so the block's abs-max needs no shuffle and
+// the scale work (table look-up, scale byte, packed operands) is paid once per block.
 template <int kFmt, int kSr, bool kEdge>
 __device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
   using C = QCfg<kFmt>;
-  const int r_base = c.tid >> 4, cv = c.tid & 15;
-  const int64_t gc = c.col0 + cv * 8;
-  const int kb = (cv * 8) / C::kBlk;
+  constexpr int kTpr = kTile / C::kBlk;                // threads per tile row
+  constexpr int kRowsPerIt = kQComputeThreads / kTpr;  // 32 or 64 rows per sweep
+  constexpr int kIts = kTile / kRowsPerIt;             // 4 or 2 sweeps
+  constexpr int kVecs = C::kBlk / 8;                   // 16-byte loads per block
+  const int r_base = c.tid / kTpr, kb = c.tid % kTpr;
+  const int64_t gc = c.col0 + kb * C::kBlk;
   const bool col_ok = !kEdge || gc < p.cols;
   const int64_t code_pitch = kFmt == kNvfp4 ? (p.cols >> 1) : p.cols;
   uint8_t* out = p.codes + (c.row0 + r_base) * code_pitch + (kFmt == kNvfp4 ? (gc >> 1) : gc);
-  const int64_t out_step = 16 * code_pitch;
-  const uint8_t* src = c.tile + r_base * 256 + cv * 16;
+  const int64_t out_step = kRowsPerIt * code_pitch;
+  const uint8_t* src = c.tile + r_base * 256 + kb * (C::kBlk * 2);
+  uint8_t* sf_dst = c.sf_row_s + (kb >> 2) * 512 + (kb & 3);
   const uint32_t seed_lo = (uint32_t)p.seed, seed_hi = (uint32_t)(p.seed >> 32);
-#pragma unroll 4
-  for (int it = 0; it < 8; ++it, out += out_step) {
-    const int r = it * 16 + r_base;
+#pragma unroll
+  for (int it = 0; it < kIts; ++it, out += out_step) {
+    const int r = it * kRowsPerIt + r_base;
     const int64_t gr = c.row0 + r;
-    const uint4 v = *reinterpret_cast<const uint4*>(src + it * 16 * 256);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    float amax = amax8(w);
-    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-    if (kFmt == kMxfp8) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    uint32_t w[kVecs][4];
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+      const uint4 q = *reinterpret_cast<const uint4*>(src + it * kRowsPerIt * 256 + v * 16);
+      w[v][0] = q.x; w[v][1] = q.y; w[v][2] = q.z; w[v][3] = q.w;
+    }
+    float amax = amax8(w[0]);
+#pragma unroll
+    for (int v = 1; v < kVecs; ++v) amax = fmaxf(amax, amax8(w[v]));
     const bool valid = !kEdge || (col_ok && gr < p.rows);
+    uint32_t sf_byte;
     if (kFmt == kNvfp4) {
       float s, rcp;
       nvfp4_scale_from_table(c.scale_tab, amax, s, rcp);
       const uint64_t rcp2 = pack2(rcp, rcp), neg2 = pack2(-s, -s);
-      float y[8];
+      uint32_t packed[2];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[j]), neg2, rcp2), y[2 * j], y[2 * j + 1]);
-      uint32_t packed;
-      if (kSr == FP4T_SR_HASH) {
-        const uint32_t e0 = (uint32_t)((gr * p.cols + gc) >> 2);
-        packed = cvt_rs_e2m1x4(y[0], y[1], y[2], y[3], hash_bits(e0, seed_lo, seed_hi)) |
-                 (cvt_rs_e2m1x4(y[4], y[5], y[6], y[7], hash_bits(e0 + 1, seed_lo, seed_hi)) << 16);
-      } else {
-        if (kSr == FP4T_SR_NOISE) {
+      for (int v = 0; v < 2; ++v) {
+        float y[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) y[j] = sr_round(y[j], valid ? __ldg(p.noise + gr * p.cols + gc + j) : 0.5f);
+        for (int j = 0; j < 4; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[v][j]), neg2, rcp2), y[2 * j], y[2 * j + 1]);
+        if (kSr == FP4T_SR_HASH) {
+          const uint32_t e0 = (uint32_t)((gr * p.cols + gc) >> 2) + 2 * v;
+          packed[v] = cvt_rs_e2m1x4(y[0], y[1], y[2], y[3], hash_bits(e0, seed_lo, seed_hi)) |
+                      (cvt_rs_e2m1x4(y[4], y[5], y[6], y[7], hash_bits(e0 + 1, seed_lo, seed_hi)) << 16);
+        } else {
+          if (kSr == FP4T_SR_NOISE) {
+            const float4* np = reinterpret_cast<const float4*>(p.noise + gr * p.cols + gc + 8 * v);
+            const float4 n0 = valid ? __ldg(np) : make_float4(0.5f, 0.5f, 0.5f, 0.5f);
+            const float4 n1 = valid ? __ldg(np + 1) : make_float4(0.5f, 0.5f, 0.5f, 0.5f);
+            y[0] = sr_round(y[0], n0.x); y[1] = sr_round(y[1], n0.y); y[2] = sr_round(y[2], n0.z); y[3] = sr_round(y[3], n0.w);
+            y[4] = sr_round(y[4], n1.x); y[5] = sr_round(y[5], n1.y); y[6] = sr_round(y[6], n1.z); y[7] = sr_round(y[7], n1.w);
+          }
+          packed[v] = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
         }
-        packed = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
       }
-      if (valid) *reinterpret_cast<uint32_t*>(out) = packed;
-      if ((cv & 1) == 0)
-        c.sf_row_s[(kb >> 2) * 512 + sf_tile_offset(r, kb)] = valid ? (uint8_t)e4m3_byte_of_scale(s) : (uint8_t)0;
+      if (valid) *reinterpret_cast<uint2*>(out) = make_uint2(packed[0], packed[1]);
+      sf_byte = e4m3_byte_of_scale(s);
     } else {
       const uint32_t sb = mx_scale_byte(amax);
       const float inv = mx_inv_scale(sb);
-      uint32_t o[2];
+      uint32_t o[8];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t w0 = w[2 * h], w1 = w[2 * h + 1];
-        o[h] = mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 << 16), inv, 0.0f),
-                                   fmaf(__uint_as_float(w0 & 0xFFFF0000u), inv, 0.0f)) |
-               (mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w1 << 16), inv, 0.0f),
-                                    fmaf(__uint_as_float(w1 & 0xFFFF0000u), inv, 0.0f)) << 16);
+      for (int v = 0; v < 4; ++v) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t w0 = w[v][2 * h], w1 = w[v][2 * h + 1];
+          o[2 * v + h] = mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 << 16), inv, 0.0f),
+                                            fmaf(__uint_as_float(w0 & 0xFFFF0000u), inv, 0.0f)) |
+                         (mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w1 << 16), inv, 0.0f),
+                                              fmaf(__uint_as_float(w1 & 0xFFFF0000u), inv, 0.0f)) << 16);
+        }
       }
-      if (valid) *reinterpret_cast<uint2*>(out) = make_uint2(o[0], o[1]);
-      if ((cv & 3) == 0) c.sf_row_s[sf_tile_offset(r, kb)] = valid ? (uint8_t)sb : (uint8_t)0;
+      if (valid) {
+        reinterpret_cast<uint4*>(out)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        reinterpret_cast<uint4*>(out)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      sf_byte = sb;
     }
+    sf_dst[sf_tile_offset(r, 0)] = valid ? (uint8_t)sf_byte : (uint8_t)0;
   }
 }
 
