@@ -37,6 +37,14 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 int sm_count();
 int sm_limit();
 
+// Dynamic tile scheduling: persistent kernels draw tile indices from a device counter so that
+// CTAs that start late (their SM was busy with another stream's kernel, e.g. a collective)
+// simply take fewer tiles.  Kernels on one stream never overlap, so each (device, stream)
+// pair owns one counter slot; returns -1 (use the static round-robin order) when the stream
+// is being captured into a graph, when the table is full or when FP4T_STATIC_TILES=1.
+constexpr int kSchedSlots = 64;
+int sched_slot_for(cudaStream_t stream);
+
 // 2-D tiled tensor map over a row-major matrix [outer, inner] of `dtype` elements whose rows
 // are row_pitch_bytes apart; out-of-range parts of a box read as zero.
 int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,

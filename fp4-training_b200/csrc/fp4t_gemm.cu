@@ -84,6 +84,7 @@ struct GemmParams {
   int out_f32;
   int vec_ok;       // 16-byte stores allowed
   int tma_ok;       // the output can be written with tiled TMA stores
+  int sched;        // tile-counter slot of the launching stream, or -1 for the static order
   int32_t* status;
 };
 
@@ -568,6 +569,20 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 // aligned falls back to per-thread stores.
 // ------------------------------------------------------------------------------------
 constexpr int kGemm2Threads = 384;
+constexpr int kSched = 4;   // depth of the in-kernel tile queue
+constexpr int kSchedReaders = 21;   // roles that read each entry: 11 in the leader CTA (with the MMA issuer), 10 in the other
+
+// {next tile, clusters done} per stream slot; both are zero between launches (the last cluster
+// to run dry puts them back)
+__device__ unsigned int g_gemm_sched[2 * kSchedSlots];
+
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// remote arrive that publishes this thread's earlier shared::cluster stores
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 
 template <int kFmt, int kBN>
 struct Cfg2 {
@@ -604,7 +619,7 @@ struct Cfg2 {
   static constexpr int kSfBoxElems = kSfChunks * 64;         // 8-byte elements per scale box row
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   static_assert(kAccStride + kBN <= kSfBuf0, "tensor memory budget");
-  static_assert((2 * kStages + 2 * kSfSlots + 4 + 2) * 8 + 8 <= 256, "barrier block (scratch words start at byte 256)");
+  static_assert((2 * kStages + 2 * kSfSlots + 4 + 2 + 2 * kSched) * 8 + 8 + 4 * kSched <= 384, "barrier block (scratch words start at byte 384)");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -676,8 +691,11 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   const uint32_t bar_sf_ready = bar_sf_free + 8 * C::kSfSlots; // [<=4] scale factors are in tensor memory (leader's copy)
   const uint32_t bar_tmem_full = bar_sf_ready + 32;            // [1]
   const uint32_t bar_tmem_empty = bar_tmem_full + 8;           // [1] (leader's copy is used)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 2 * C::kSfSlots + 6);
+  const uint32_t bar_sched_full = bar_tmem_empty + 8;          // [kSched] a tile index was published (own copy)
+  const uint32_t bar_sched_empty = bar_sched_full + 8 * kSched;  // [kSched] every role of both CTAs read it (leader's copy)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 2 * C::kSfSlots + 6 + 2 * kSched);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [kSched]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -698,6 +716,10 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     for (int b = 0; b < C::kSfBufs; ++b) mbar_init(bar_sf_ready + 8 * b, 8);   // four scale warps in each CTA
     mbar_init(bar_tmem_full, 1);
     mbar_init(bar_tmem_empty, 8);          // four epilogue warps in each CTA
+    for (int q = 0; q < kSched; ++q) {
+      mbar_init(bar_sched_full + 8 * q, 1);
+      mbar_init(bar_sched_empty + 8 * q, kSchedReaders);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -719,14 +741,68 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   const uint32_t leader_full = mapa_u32(bar_full, 0);
   const uint32_t leader_tmem_empty = mapa_u32(bar_tmem_empty, 0);
   const uint32_t leader_sf_ready = mapa_u32(bar_sf_ready, 0);
+  const uint32_t leader_sched_empty = mapa_u32(bar_sched_empty, 0);
 
-  if (warp == 0) {
+  // Next tile of this CTA pair, for the n-th iteration of a role's tile loop (one thread per
+  // role calls it): wait for the queue entry, read it, hand the entry back.  The arrive is
+  // made to depend on the value read so that the entry cannot be reused before the load returned.
+  auto sched_next = [&](uint32_t n, int code) -> int {
+    const uint32_t q = n % kSched;
+    if (!mbar_try_cluster(bar_sched_full + 8 * q, (n / kSched) & 1u) &&
+        !mbar_wait_cluster(bar_sched_full + 8 * q, (n / kSched) & 1u, abort_flag, g.status, code))
+      return -1;
+    const int tile = sched_tile[q];
+    if (tile >= -1) mbar_arrive_cluster(leader_sched_empty + 8 * q);
+    return tile;
+  };
+
+  if (warp == 2) {
+   if (lane == 0 && leader) {
+    // ------------------------------ tile scheduler (leader CTA) ------------------------------
+    // Publishes tile indices to both CTAs, a few tiles ahead of the roles that consume them:
+    // drawn from the stream's device counter (clusters that start late take fewer tiles), or
+    // the static round-robin order when no counter slot is given.
+    const uint32_t peer_sched_full = mapa_u32(bar_sched_full, 1);
+    const uint32_t peer_sched_tile = mapa_u32(smem_u32(const_cast<int*>(sched_tile)), 1);
+    for (uint32_t n = 0;; ++n) {
+      const uint32_t q = n % kSched;
+      if (n >= (uint32_t)kSched &&
+          !mbar_wait(bar_sched_empty + 8 * q, ((n / kSched) - 1u) & 1u, abort_flag, g.status, 30))
+        break;
+      int tile;
+      if (g.sched >= 0) {
+        const unsigned int t = atomicAdd(&g_gemm_sched[2 * g.sched], 1u);
+        tile = t < (unsigned int)num_tiles ? (int)t : -1;
+      } else {
+        const int t = cluster_id + (int)n * num_clusters;
+        tile = t < num_tiles ? t : -1;
+      }
+      sched_tile[q] = tile;
+      st_shared_cluster_u32(peer_sched_tile + 4 * q, (uint32_t)tile);
+      mbar_arrive(bar_sched_full + 8 * q);
+      mbar_arrive_release_cluster(peer_sched_full + 8 * q);
+      if (tile < 0) {
+        if (g.sched >= 0) {   // the last cluster to run dry zeroes the counters for the next launch
+          const unsigned int d = atomicAdd(&g_gemm_sched[2 * g.sched + 1], 1u);
+          if (d == (unsigned int)num_clusters - 1u) {
+            atomicExch(&g_gemm_sched[2 * g.sched], 0u);
+            atomicExch(&g_gemm_sched[2 * g.sched + 1], 0u);
+          }
+        }
+        break;
+      }
+    }
+   }
+   __syncwarp();
+  } else if (warp == 0) {
    if (lane == 0) {
     // ------------------------------ operand producer (both CTAs) ------------------------------
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+    for (uint32_t tn = 0; ok; ++tn) {
+      const int tile = sched_next(tn, 31);
+      if (tile < 0) break;
       const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
       const int row_p = (pm * 2 + (int)rank) * kBM;           // this CTA's 128-row tile of P
       const int row_q = n_idx * kBN + (int)rank * (kBN / 2);  // this CTA's half of the Q rows
@@ -755,7 +831,9 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     int slot = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+    for (uint32_t tn = 0; ok; ++tn) {
+      const int tile = sched_next(tn, 32);
+      if (tile < 0) break;
       const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
       const int m_tile = pm * 2 + (int)rank;
       for (int ks = 0; ks < g.k_stages; ++ks) {
@@ -788,7 +866,8 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     uint32_t k = 0;          // stages issued so far; selects the scale-factor buffer
     int it = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+    for (; ok; ++it) {
+      if (sched_next((uint32_t)it, 33) < 0) break;
       if (it > 0) {
         if (!mbar_wait(bar_tmem_empty, (uint32_t)((it - 1) & 1), abort_flag, g.status, 22)) { ok = false; break; }
         tc_fence_after();
@@ -828,10 +907,14 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   } else if (warp >= 8) {
     // ------------------------------ scale-factor warps (both CTAs) ------------------------------
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t sf_scratch = bar_full + 256 + 4 * (warp & 3);   // unused tail of the barrier block
+    const uint32_t sf_scratch = bar_full + 384 + 4 * (warp & 3);   // unused tail of the barrier block
     uint32_t k = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+    for (uint32_t tn = 0; ok; ++tn) {
+      int tile = 0;
+      if (lane == 0) tile = sched_next(tn, 34);
+      tile = __shfl_sync(0xFFFFFFFFu, tile, 0);
+      if (tile < 0) break;
       for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
         const uint32_t slot = k % C::kSfSlots, use = k / C::kSfSlots;
         if (!mbar_wait(bar_sf_land + 8 * slot, use & 1u, abort_flag, g.status, 26)) { ok = false; break; }
@@ -885,7 +968,11 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
     uint8_t* epi_buf = smem_gen + C::kEpi0 + quad * 4096;
     uint32_t n_emit = 0;
     int it = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
+    for (;; ++it) {
+      int tile = 0;
+      if (lane == 0) tile = sched_next((uint32_t)it, 35);
+      tile = __shfl_sync(0xFFFFFFFFu, tile, 0);
+      if (tile < 0) break;
       const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
       int ok = 1;
       if (lane == 0) ok = mbar_wait(bar_tmem_full, (uint32_t)(it & 1), abort_flag, g.status, 24) ? 1 : 0;
@@ -1111,6 +1198,7 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
   g.vec_ok = (reinterpret_cast<uintptr_t>(d) % 16 == 0) && ((ldd * esz) % 16 == 0) &&
              (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
   g.tma_ok = (reinterpret_cast<uintptr_t>(d) % 16 == 0) && ((ldd * esz) % 16 == 0);
+  g.sched = sched_slot_for(stream);
   g.status = status;
   g.n_tiles = 0;
 

@@ -3,6 +3,8 @@
 // arithmetic; they exist for operand forms the reference's op signatures accept and the
 // fused quantizers do not already produce.
 #include <atomic>
+#include <cstdlib>
+#include <mutex>
 #include <cstdarg>
 #include <cstdio>
 
@@ -29,6 +31,28 @@ int32_t* current_status_word() { return g_status_word; }
 
 static std::atomic<int> g_sm_limit{0};
 int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
+
+int sched_slot_for(cudaStream_t stream) {
+  static const bool force_static = [] { const char* e = getenv("FP4T_STATIC_TILES"); return e && e[0] == '1'; }();
+  if (force_static) return -1;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return -1;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  struct Key { int dev; cudaStream_t stream; };
+  static std::mutex mu;
+  static Key keys[kSchedSlots];
+  static int used = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (keys[i].dev == dev && keys[i].stream == stream) return i;
+  if (used == kSchedSlots) return -1;
+  keys[used] = Key{dev, stream};
+  return used++;
+}
 
 int sm_count() {
   static int cached[64] = {0};

@@ -60,6 +60,35 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try(bar, parity)) return true;   // try_wait itself blocks for a while; two tries cover most waits
   return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
+// The same wait with acquire semantics at cluster scope: for data another CTA of the cluster
+// wrote into this CTA's shared memory before its (release.cluster) arrive.
+__device__ __forceinline__ uint32_t mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                      int32_t* status, int code) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_cluster(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

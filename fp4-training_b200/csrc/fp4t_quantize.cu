@@ -81,8 +81,17 @@ __device__ __forceinline__ uint32_t cvt_rs_e2m1x4(float e0, float e1, float e2, 
       : "f"(e0), "f"(e1), "f"(e2), "f"(e3), "r"(rbits));
   return out;
 }
-__device__ __forceinline__ uint32_t hash_bits(uint32_t idx, uint32_t seed_lo, uint32_t seed_hi) {
-  return mix32(idx * 0x9E3779B9u + seed_lo) ^ seed_hi;
+// Random bits for eight elements (two cvt.rs words) from the index of the 8-element group:
+// a Weyl step, one multiply-xorshift round for the first word and one more multiply-xorshift
+// for the second.  Bit means are within 1e-3 of 1/2 and the lag-1 correlation between
+// neighbouring groups is below 1e-2 (checked on the host over 4M indices).
+__device__ __forceinline__ uint32_t hash_pair(uint32_t idx8, uint32_t seed_lo, uint32_t seed_hi, uint32_t& second) {
+  uint32_t h = idx8 * 0x9E3779B9u + seed_lo;
+  h ^= h >> 16; h *= 0x7FEB352Du; h ^= h >> 15;
+  h ^= seed_hi;
+  uint32_t t = h * 0x846CA68Bu;
+  second = t ^ (t >> 16);
+  return h;
 }
 __device__ __forceinline__ float amax8(const uint32_t (&w)[4]) {
   const float m0 = fmaxf(fabsf(__uint_as_float(w[0] << 16)), fabsf(__uint_as_float(w[0] & 0xFFFF0000u)));
@@ -147,9 +156,9 @@ __device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[v][j]), neg2, rcp2), y[2 * j], y[2 * j + 1]);
         if (kSr == FP4T_SR_HASH) {
-          const uint32_t e0 = (uint32_t)((gr * p.cols + gc) >> 2) + 2 * v;
-          packed[v] = cvt_rs_e2m1x4(y[0], y[1], y[2], y[3], hash_bits(e0, seed_lo, seed_hi)) |
-                      (cvt_rs_e2m1x4(y[4], y[5], y[6], y[7], hash_bits(e0 + 1, seed_lo, seed_hi)) << 16);
+          uint32_t h1;
+          const uint32_t h0 = hash_pair((uint32_t)((gr * p.cols + gc) >> 3) + v, seed_lo, seed_hi, h1);
+          packed[v] = cvt_rs_e2m1x4(y[0], y[1], y[2], y[3], h0) | (cvt_rs_e2m1x4(y[4], y[5], y[6], y[7], h1) << 16);
         } else {
           if (kSr == FP4T_SR_NOISE) {
             const float4* np = reinterpret_cast<const float4*>(p.noise + gr * p.cols + gc + 8 * v);
@@ -230,13 +239,13 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
         }
         uint32_t a8, b8;
         if (kSr == FP4T_SR_HASH) {
-          const uint32_t rg = (uint32_t)((gr0 + h * 16 + g8 * 8) >> 2);
-          const uint32_t i0 = rg * (uint32_t)p.cols + (uint32_t)gcA;
-          const uint32_t i1 = i0 + (uint32_t)p.cols;
-          a8 = cvt_rs_e2m1x4(yA[0], yA[1], yA[2], yA[3], hash_bits(i0, seed_lo, seed_hi)) |
-               (cvt_rs_e2m1x4(yA[4], yA[5], yA[6], yA[7], hash_bits(i1, seed_lo, seed_hi)) << 16);
-          b8 = cvt_rs_e2m1x4(yB[0], yB[1], yB[2], yB[3], hash_bits(i0 + 1, seed_lo, seed_hi)) |
-               (cvt_rs_e2m1x4(yB[4], yB[5], yB[6], yB[7], hash_bits(i1 + 1, seed_lo, seed_hi)) << 16);
+          // one index per (8 rows, column) group of the transposed tensor
+          const uint32_t i0 = (uint32_t)((gr0 + h * 16 + g8 * 8) >> 3) * (uint32_t)p.cols + (uint32_t)gcA;
+          uint32_t a1, b1;
+          const uint32_t a0 = hash_pair(i0, seed_lo, seed_hi, a1);
+          const uint32_t b0 = hash_pair(i0 + 1, seed_lo, seed_hi, b1);
+          a8 = cvt_rs_e2m1x4(yA[0], yA[1], yA[2], yA[3], a0) | (cvt_rs_e2m1x4(yA[4], yA[5], yA[6], yA[7], a1) << 16);
+          b8 = cvt_rs_e2m1x4(yB[0], yB[1], yB[2], yB[3], b0) | (cvt_rs_e2m1x4(yB[4], yB[5], yB[6], yB[7], b1) << 16);
         } else {
           if (kSr == FP4T_SR_NOISE) {
 #pragma unroll
@@ -310,10 +319,13 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
   }
 }
 
+// {next tile, CTAs done} per stream slot; zero between launches (the last CTA to run dry resets them)
+__device__ unsigned int g_quant_sched[2 * kSchedSlots];
+
 template <int kFmt, int kSr, bool kColsum>
 __global__ void __launch_bounds__(kQThreads, 2)
 quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, const int tiles_x,
-                    const int num_tiles, int32_t* status) {
+                    const int num_tiles, const int sched, int32_t* status) {
   using C = QCfg<kFmt>;
   extern __shared__ uint8_t q_smem_raw[];
   const uint32_t base = (smem_u32(q_smem_raw) + 127u) & ~127u;
@@ -323,6 +335,7 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kQStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kQStages);
+  volatile int* tile_of_stage = abort_flag + 1;   // [kQStages] tile index the producer put into each stage (-1: no more)
   float2* scale_tab = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(bars) + 64);
   float* colsum_stage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 64 + 1024);   // [2][4][128]
 
@@ -345,10 +358,32 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
   if (warp == kQComputeThreads / 32) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
+      // Tiles come from the stream's device counter (a CTA that starts late, because its SM was
+      // busy with another stream's kernel, takes fewer) or in the static round-robin order.
       int stage = 0;
       uint32_t phase = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      for (uint32_t n = 0;; ++n) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status, 11)) break;
+        int t;
+        if (sched >= 0) {
+          const unsigned int d = atomicAdd(&g_quant_sched[2 * sched], 1u);
+          t = d < (unsigned int)num_tiles ? (int)d : -1;
+        } else {
+          const int64_t d = (int64_t)blockIdx.x + (int64_t)n * gridDim.x;
+          t = d < num_tiles ? (int)d : -1;
+        }
+        tile_of_stage[stage] = t;
+        if (t < 0) {
+          mbar_arrive(bar_full + 8 * stage);   // publishes the end marker
+          if (sched >= 0) {
+            const unsigned int d = atomicAdd(&g_quant_sched[2 * sched + 1], 1u);
+            if (d == gridDim.x - 1u) {
+              atomicExch(&g_quant_sched[2 * sched], 0u);
+              atomicExch(&g_quant_sched[2 * sched + 1], 0u);
+            }
+          }
+          break;
+        }
         const int ty = t / tiles_x, tx = t - ty * tiles_x;
         mbar_expect_tx(bar_full + 8 * stage, kQTileBytes);
         tma_load_2d(base + stage * kQTileBytes, &map_x, bar_full + 8 * stage, tx * kTile, ty * kTile);
@@ -367,12 +402,14 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
   int stage = 0;
   uint32_t phase = 0;
   int buf = 0;
-  for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+  for (;;) {
+    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 12)) break;
+    const int t = tile_of_stage[stage];
+    if (t < 0) break;
     const int ty = t / tiles_x, tx = t - ty * tiles_x;
     TileCtx c;
     c.row0 = (int64_t)ty * kTile;
     c.col0 = (int64_t)tx * kTile;
-    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 12)) break;
     c.tile = gen + stage * kQTileBytes;
     c.sf_row_s = sf_stage + buf * 2 * C::kSfStage;
     c.sf_col_s = c.sf_row_s + C::kSfStage;
@@ -603,11 +640,12 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   if (rc != FP4T_OK) return rc;
   const int grid = num_tiles < 2 * sms ? num_tiles : 2 * sms;
   int32_t* status = current_status_word();
+  const int sched = sched_slot_for(stream);
 #define FP4T_LAUNCH_Q2(FMT, SR, CS)                                                                        \
   do {                                                                                                     \
     auto kern = quantize_tma_kernel<FMT, SR, CS>;                                                          \
     FP4T_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<FMT>::kSmemBytes)); \
-    kern<<<grid, kQThreads, QCfg<FMT>::kSmemBytes, stream>>>(map_x, p, (int)tiles_x, num_tiles, status);   \
+    kern<<<grid, kQThreads, QCfg<FMT>::kSmemBytes, stream>>>(map_x, p, (int)tiles_x, num_tiles, sched, status); \
   } while (0)
 #define FP4T_LAUNCH_Q(FMT, SR)                  \
   do {                                          \
