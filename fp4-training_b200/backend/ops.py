@@ -60,7 +60,10 @@ def check_status(device="cuda") -> None:
     code = int(s[0].item())
     if code != 0:
         s.zero_()
-        raise RuntimeError(f"fp4t GEMM kernel abandoned a wait (role code {code})")
+        # a kernel that gave up may have left its tile counters nonzero
+        with torch.cuda.device(s.device):
+            _lib.check(_lib.lib().fp4t_reset_tile_counters(_lib.stream_ptr(s.device)))
+        raise RuntimeError(f"fp4t kernel abandoned a wait (role code {code})")
 
 
 def _alloc_q(outer, inner, blk, packed, device):

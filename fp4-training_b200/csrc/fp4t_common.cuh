@@ -44,6 +44,8 @@ int sm_limit();
 // is being captured into a graph, when the table is full or when FP4T_STATIC_TILES=1.
 constexpr int kSchedSlots = 64;
 int sched_slot_for(cudaStream_t stream);
+int reset_gemm_tile_counters(cudaStream_t stream);      // fp4t_gemm.cu
+int reset_quantize_tile_counters(cudaStream_t stream);  // fp4t_quantize.cu
 
 // 2-D tiled tensor map over a row-major matrix [outer, inner] of `dtype` elements whose rows
 // are row_pitch_bytes apart; out-of-range parts of a box read as zero.

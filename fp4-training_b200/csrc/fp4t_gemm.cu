@@ -1225,6 +1225,13 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
 }
 
 }  // namespace
+
+int reset_gemm_tile_counters(cudaStream_t stream) {
+  void* addr = nullptr;
+  FP4T_CUDA(cudaGetSymbolAddress(&addr, g_gemm_sched));
+  FP4T_CUDA(cudaMemsetAsync(addr, 0, sizeof(unsigned int) * 2 * kSchedSlots, stream));
+  return FP4T_OK;
+}
 }  // namespace fp4t
 
 extern "C" int fp4t_gemm_nvfp4(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,

@@ -199,6 +199,12 @@ using namespace fp4t;
 extern "C" const char* fp4t_last_error(void) { return fp4t::g_error; }
 extern "C" int fp4t_version(void) { return 101; }
 
+extern "C" int fp4t_reset_tile_counters(fp4t_stream_t stream) {
+  int rc = fp4t::reset_gemm_tile_counters(reinterpret_cast<cudaStream_t>(stream));
+  if (rc != FP4T_OK) return rc;
+  return fp4t::reset_quantize_tile_counters(reinterpret_cast<cudaStream_t>(stream));
+}
+
 extern "C" int fp4t_set_sm_limit(int sms) {
   FP4T_REQUIRE(sms >= 0, "fp4t_set_sm_limit: negative limit");
   fp4t::g_sm_limit.store(sms, std::memory_order_relaxed);

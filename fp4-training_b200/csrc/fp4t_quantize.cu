@@ -690,6 +690,13 @@ int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64
 }
 
 }  // namespace
+
+int reset_quantize_tile_counters(cudaStream_t stream) {
+  void* addr = nullptr;
+  FP4T_CUDA(cudaGetSymbolAddress(&addr, g_quant_sched));
+  FP4T_CUDA(cudaMemsetAsync(addr, 0, sizeof(unsigned int) * 2 * kSchedSlots, stream));
+  return FP4T_OK;
+}
 }  // namespace fp4t
 
 extern "C" int fp4t_quantize_nvfp4_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,

@@ -78,6 +78,14 @@ FP4T_API int fp4t_set_status_word(int32_t* device_word);
  */
 FP4T_API int fp4t_set_sm_limit(int sms);
 
+/*
+ * The persistent kernels draw their tiles from per-stream device counters that every launch
+ * leaves at zero.  A launch that gave up on a wait (nonzero status word) may leave them
+ * nonzero; this puts all counters of the current device back to zero (stream-ordered on
+ * `stream`).  No counterpart in the reference.
+ */
+FP4T_API int fp4t_reset_tile_counters(fp4t_stream_t stream);
+
 /* Bytes of the swizzled scale buffer for a logical [outer, kblocks] scale matrix. */
 FP4T_API int64_t fp4t_sf_bytes(int64_t outer, int64_t kblocks);
 

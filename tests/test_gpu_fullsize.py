@@ -152,3 +152,20 @@ def test_gemm_is_deterministic(ops, fmt, m, n, k, dtype):
         again = gemm(ac, asf, bc, bsf, None, dtype)
         assert torch.equal(again, first)
     ops.check_status()
+
+
+def test_tile_counter_reset_keeps_results(ops):
+    """fp4t_reset_tile_counters zeroes the per-stream tile counters (what a host does after a launch
+    reported a timed-out wait); launches after it give the same bits as before."""
+    from backend import _lib
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    a = torch.randn(1024, 2048, device="cuda", generator=gen).to(torch.bfloat16)
+    b = torch.randn(768, 2048, device="cuda", generator=gen).to(torch.bfloat16)
+    ac, asf, _, _ = ops.quantize_nvfp4(a, True, False)
+    bc, bsf, _, _ = ops.quantize_nvfp4(b, True, False)
+    first = ops.gemm_nvfp4(ac, asf, bc, bsf, None, torch.float32).clone()
+    _lib.check(_lib.lib().fp4t_reset_tile_counters(_lib.stream_ptr(a.device)))
+    ac2, asf2, _, _ = ops.quantize_nvfp4(a, True, False)
+    assert torch.equal(ac, ac2) and torch.equal(asf, asf2)
+    assert torch.equal(ops.gemm_nvfp4(ac, asf, bc, bsf, None, torch.float32), first)
+    ops.check_status()
