@@ -62,7 +62,7 @@ def check_status(device="cuda") -> None:
         s.zero_()
         # a kernel that gave up may have left its tile counters nonzero
         with torch.cuda.device(s.device):
-            _lib.check(_lib.lib().fp4t_reset_tile_counters(_lib.stream_ptr(s.device)))
+            _lib.check(_lib.lib().fp4t_reset_tile_counters(_lib.stream_ptr(s.device)), "fp4t_reset_tile_counters")
         raise RuntimeError(f"fp4t kernel abandoned a wait (role code {code})")
 
 

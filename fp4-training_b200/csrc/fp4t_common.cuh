@@ -44,6 +44,14 @@ int sm_limit();
 // is being captured into a graph, when the table is full or when FP4T_STATIC_TILES=1.
 constexpr int kSchedSlots = 64;
 int sched_slot_for(cudaStream_t stream);
+
+// Launch attribute that lets a kernel start under the tail of its predecessor (the kernel must
+// call griddepcontrol.wait before it touches global memory).  FP4T_NO_PDL=1 switches it off.
+bool pdl_enabled();
+inline void pdl_attribute(cudaLaunchAttribute* attr) {
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+}
 int reset_gemm_tile_counters(cudaStream_t stream);      // fp4t_gemm.cu
 int reset_quantize_tile_counters(cudaStream_t stream);  // fp4t_quantize.cu
 

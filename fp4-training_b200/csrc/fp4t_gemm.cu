@@ -678,7 +678,9 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   extern __shared__ __align__(1024) uint8_t smem_pair[];
   uint8_t* smem_gen = smem_pair;
   const uint32_t smem_base = smem_u32(smem_pair);
+  pdl_launch_dependents();   // the next kernel in the stream may set itself up under this one's tail
   if (smem_base & 1023u) {   // the swizzled tiles need the alignment the declaration asks for
+    pdl_wait();
     if (threadIdx.x == 0 && g.status) atomicCAS(g.status, 0, 29);
     return;
   }
@@ -734,6 +736,9 @@ gemm2_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid
   cluster_sync_all();       // barriers of both CTAs are initialised before any remote arrive
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only this CTA pair's shared and tensor memory; from here on the
+  // kernel reads its operands and the tile counter, so the predecessor has to be complete.
+  pdl_wait();
 
   // pair tile = 256 rows x kBN columns
   const int pair_m_tiles = (g.m_tiles + 1) >> 1;
@@ -1145,13 +1150,14 @@ int launch_gemm2(const void* p_codes, const void* q_codes, const GemmParams& g0,
   cfg.blockDim = dim3(kGemm2Threads, 1, 1);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  pdl_attribute(&attr[1]);
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
   FP4T_CUDA(cudaLaunchKernelEx(&cfg, kern, map_p, map_q, map_psf, map_qsf, map_d, g));
   return FP4T_OK;
 }

@@ -32,6 +32,11 @@ int32_t* current_status_word() { return g_status_word; }
 static std::atomic<int> g_sm_limit{0};
 int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
 
+bool pdl_enabled() {
+  static const bool off = [] { const char* e = getenv("FP4T_NO_PDL"); return e && e[0] == '1'; }();
+  return !off;
+}
+
 int sched_slot_for(cudaStream_t stream) {
   static const bool force_static = [] { const char* e = getenv("FP4T_STATIC_TILES"); return e && e[0] == '1'; }();
   if (force_static) return -1;

@@ -120,4 +120,12 @@ __device__ __forceinline__ void bulk_wait_all() {
 // orders this thread's shared-memory writes before later async-proxy (TMA) reads of them
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may begin while its predecessor in the stream still runs.  `pdl_launch_dependents`
+// lets the successor's CTAs be scheduled as soon as resources free up; `pdl_wait` returns once
+// the predecessor has completed and its memory is visible -- nothing the predecessor wrote (or
+// still reads) may be touched before it.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 }  // namespace fp4t

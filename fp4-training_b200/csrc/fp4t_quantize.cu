@@ -341,6 +341,7 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
   if (kFmt == kNvfp4 && tid < 128) scale_tab[tid] = make_float2(kScaleTable.v[tid].s, kScaleTable.v[tid].r);
   if (tid == 0) {
     for (int s = 0; s < kQStages; ++s) {
@@ -351,6 +352,7 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  pdl_wait();   // the input (and the tile counter) belong to the predecessor until it is complete
 
   const bool want_row = p.codes != nullptr;
   const bool want_col = p.codes_t != nullptr;
@@ -562,6 +564,8 @@ __global__ void colsum_generic_kernel(const TIn* __restrict__ x, int64_t rows, i
 // fp32 accumulator -> bias gradient in the caller's dtype.
 __global__ void colsum_finalize_kernel(const float* __restrict__ colsum, void* __restrict__ out, int out_f32,
                                        int64_t cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   if (out_f32) static_cast<float*>(out)[c] = colsum[c];
@@ -645,7 +649,16 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   do {                                                                                                     \
     auto kern = quantize_tma_kernel<FMT, SR, CS>;                                                          \
     FP4T_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<FMT>::kSmemBytes)); \
-    kern<<<grid, kQThreads, QCfg<FMT>::kSmemBytes, stream>>>(map_x, p, (int)tiles_x, num_tiles, sched, status); \
+    cudaLaunchConfig_t cfg = {};                                                                           \
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);                                                              \
+    cfg.blockDim = dim3(kQThreads, 1, 1);                                                                  \
+    cfg.dynamicSmemBytes = QCfg<FMT>::kSmemBytes;                                                          \
+    cfg.stream = stream;                                                                                   \
+    cudaLaunchAttribute attr;                                                                              \
+    pdl_attribute(&attr);                                                                                  \
+    cfg.attrs = &attr;                                                                                     \
+    cfg.numAttrs = 1;                                                                                      \
+    FP4T_CUDA(cudaLaunchKernelEx(&cfg, kern, map_x, p, (int)tiles_x, num_tiles, sched, status));           \
   } while (0)
 #define FP4T_LAUNCH_Q(FMT, SR)                  \
   do {                                          \
@@ -683,9 +696,18 @@ int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64
                                            noise_t, seed, colsum_scratch, stream);
     if (rc != FP4T_OK) return rc;
   }
-  colsum_finalize_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, stream>>>(colsum_scratch, bias_grad,
-                                                                           bias_grad_dtype == FP4T_DT_F32, cols);
-  FP4T_CUDA(cudaGetLastError());
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ceil_div(cols, 256), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    pdl_attribute(&attr);
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    FP4T_CUDA(cudaLaunchKernelEx(&cfg, colsum_finalize_kernel, static_cast<const float*>(colsum_scratch), bias_grad,
+                                 (int)(bias_grad_dtype == FP4T_DT_F32), cols));
+  }
   return FP4T_OK;
 }
 

@@ -164,8 +164,30 @@ def test_tile_counter_reset_keeps_results(ops):
     ac, asf, _, _ = ops.quantize_nvfp4(a, True, False)
     bc, bsf, _, _ = ops.quantize_nvfp4(b, True, False)
     first = ops.gemm_nvfp4(ac, asf, bc, bsf, None, torch.float32).clone()
-    _lib.check(_lib.lib().fp4t_reset_tile_counters(_lib.stream_ptr(a.device)))
+    _lib.check(_lib.lib().fp4t_reset_tile_counters(_lib.stream_ptr(a.device)), "fp4t_reset_tile_counters")
     ac2, asf2, _, _ = ops.quantize_nvfp4(a, True, False)
     assert torch.equal(ac, ac2) and torch.equal(asf, asf2)
     assert torch.equal(ops.gemm_nvfp4(ac, asf, bc, bsf, None, torch.float32), first)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8"])
+def test_chained_layer_calls_are_deterministic(ops, fmt):
+    """Forward + backward of one layer is six kernels launched back to back, each allowed to set
+    itself up under the tail of its predecessor (programmatic dependent launch) and each drawing
+    its tiles dynamically.  Repeating the chain on the same inputs must give the same bits: a
+    kernel that touched its predecessor's output before that kernel completed would show here."""
+    n, ic, oc = 4096, 2048, 3072
+    x, w, g = _inputs(n, ic, oc, 3)
+    bias = (torch.randn(oc, device="cuda") * 0.1).to(torch.bfloat16)
+    ref = None
+    for _ in range(8):
+        y, ws = ops.linear_forward(fmt, x, w, bias, True, True, torch.bfloat16)
+        dx, dw, db = ops.linear_backward(fmt, g, ws, ic, True, True, True, sr=ops.SR_HASH, seed=7)
+        cur = (y.clone(), dx.clone(), dw.clone())
+        if ref is None:
+            ref = cur
+        else:
+            for a, b in zip(cur, ref):
+                assert torch.equal(a, b)
     ops.check_status()
