@@ -196,7 +196,22 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # weight and bias gradients land in one flat buffer (two of them, rotating) so that a single
     # NCCL all-reduce per step, on a side stream, can overlap the kernels of step i+1, as it
     # does under the backward pass of the previous layer in data-parallel training
-    grad_bufs = [torch.empty(OC * IC + OC, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    reducers = None
+    if world > 1 and os.environ.get("FP4T_ALLREDUCE", "nccl") == "switch":
+        # the library's own in-switch all-reduce (opt-in: measured a few per cent behind NCCL inside
+        # the step); NCCL if these GPUs offer no NVLink multicast
+        try:
+            from dp import SwitchAllReducer
+            reducers = [SwitchAllReducer(OC * IC + OC, dev, ctas=int(os.environ.get("FP4T_ALLREDUCE_CTAS", "148")))
+                        for _ in range(2)]
+        except Exception as e:   # noqa: BLE001
+            if rank == 0:
+                print(f"bench: in-switch all-reduce unavailable ({e!r}); using NCCL", file=sys.stderr)
+            reducers = None
+    if reducers is not None:
+        grad_bufs = [r.flat for r in reducers]
+    else:
+        grad_bufs = [torch.empty(OC * IC + OC, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
     comm_done = [None, None]
 
@@ -214,7 +229,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             ready.record()
             with torch.cuda.stream(comm_stream):
                 comm_stream.wait_event(ready)
-                dist.all_reduce(flat)
+                if reducers is not None:
+                    reducers[slot].all_reduce(ops.status_word(dev))
+                    ops.LAUNCHES["allreduce"] += 1
+                else:
+                    dist.all_reduce(flat)
                 comm_done[slot] = ev()
                 comm_done[slot].record()
         return y, dx, dw, db
@@ -235,8 +254,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     t_start, t_end = ev(enable_timing=True), ev(enable_timing=True)
     barrier()
     t_start.record()
+    host_t0 = time.perf_counter()
     for i in range(args.steps):
         hot_step(i)
+    host_enqueue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps   # CPU time to enqueue one step
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
@@ -280,6 +301,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate, bf16 out)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "l2": "inputs larger than L2 (160 MB bf16 per step, two sets rotated)",
                    "parallelism": f"dp{world}" if world > 1 else "single",
+                   "allreduce": ("none" if world == 1 else
+                                 "fp4t in-switch multimem kernel on a side stream, one call per step" if reducers is not None
+                                 else "NCCL on a side stream, one call per step"),
                    "bias_grad": "fused into the dY quantizer (fp32 atomics + finishing kernel)",
                    "frac_of_nominal_fp4_peak": value / world / FP4_NOMINAL_TFLOPS},
         "roofline": {"bound": "tensor", "kernel": "gemm2_blockscaled_kernel<nvfp4, 256> two-CTA (fprop+dgrad+wgrad)",
@@ -297,6 +321,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                 "api": "custom.CublasltNvfp4Linear forward+backward under bf16 autocast"},
         "gpu_launches": launches,
+        "host_enqueue_ms_per_step": host_enqueue_ms,
         "clocks": clocks,
     }
     if cpu is not None:

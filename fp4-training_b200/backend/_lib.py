@@ -27,6 +27,9 @@ _SIGNATURES = {
     "fp4t_set_status_word": (ctypes.c_int, [_c_vp]),
     "fp4t_set_sm_limit": (ctypes.c_int, [ctypes.c_int]),
     "fp4t_reset_tile_counters": (ctypes.c_int, [ctypes.c_void_p]),
+    "fp4t_allreduce_sum_bf16_multimem": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                                       ctypes.c_int, ctypes.c_int64, ctypes.c_uint32, ctypes.c_int,
+                                                       ctypes.c_void_p, ctypes.c_void_p]),
     "fp4t_quantize_nvfp4": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
                                             ctypes.c_int, _c_vp, _c_vp, ctypes.c_uint64, _c_vp]),
     "fp4t_quantize_mxfp8": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,

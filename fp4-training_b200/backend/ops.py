@@ -21,7 +21,7 @@ import threading
 
 _status = {}
 _tls = threading.local()
-LAUNCHES = {"quantize": 0, "gemm": 0, "misc": 0}   # kernels enqueued by this process
+LAUNCHES = {"quantize": 0, "gemm": 0, "misc": 0, "allreduce": 0}   # kernels enqueued by this process
 
 
 def _need_cuda(*tensors):

@@ -8,8 +8,15 @@ registration order (the order backward produces their gradients), a bucket's all
 launched asynchronously as soon as its last gradient has been accumulated, so the reduction of
 late layers overlaps the backward pass of earlier ones, and `finish()` waits for all buckets
 and writes the averaged gradients back.
+
+`SwitchAllReducer` is the exchange for one flat bf16 gradient buffer on GPUs that share an
+NVSwitch: the buffer lives in symmetric memory bound to an NVLink multicast object and is summed
+in place by `fp4t_allreduce_sum_bf16_multimem` (reduction inside the switch, a kernel small
+enough to be resident beside the persistent quantizers and GEMMs it overlaps with).
 """
 from __future__ import annotations
+
+import ctypes
 
 import torch
 import torch.distributed as dist
@@ -95,3 +102,46 @@ def broadcast_parameters(module: torch.nn.Module, src: int = 0, process_group=No
         return
     for t in list(module.parameters()) + list(module.buffers()):
         dist.broadcast(t.data, src=src, group=process_group)
+
+
+class SwitchAllReducer:
+    """In-place sum all-reduce of `self.flat` (bf16, `numel` rounded up to a multiple of 8) over
+    the ranks of `process_group`, all on one NVSwitch domain.  Every rank constructs it with the
+    same arguments and calls `all_reduce()` the same number of times; the call is asynchronous on
+    the current stream.  Raises at construction if the GPUs offer no NVLink multicast."""
+
+    def __init__(self, numel: int, device, process_group=None, ctas: int = 148):
+        import torch.distributed._symmetric_memory as symm_mem
+        from backend import _lib
+        self._lib = _lib
+        group = process_group if process_group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("SwitchAllReducer handles at most 8 ranks")
+        self.device = torch.device(device)
+        self.numel = (numel + 7) // 8 * 8
+        self.ctas = ctas
+        self.flat = symm_mem.empty(self.numel, dtype=torch.bfloat16, device=self.device)
+        self.flat.zero_()
+        self._handle = symm_mem.rendezvous(self.flat, group.group_name)
+        if not getattr(self._handle, "multicast_ptr", 0):
+            raise RuntimeError("symmetric memory has no multicast address on these GPUs")
+        flag_words = 256 * 8          # FP4T_ALLREDUCE_FLAG_WORDS
+        self._flags = symm_mem.empty(flag_words, dtype=torch.int32, device=self.device)
+        self._flags.zero_()
+        self._flag_handle = symm_mem.rendezvous(self._flags, group.group_name)
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self._flag_handle.buffer_ptrs])
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)           # every rank's flags are zero before anyone's first call
+        self._epoch = 0
+
+    def all_reduce(self, status=None):
+        """Sum `self.flat` over the ranks, in place, on the current stream of `self.device`."""
+        self._epoch += 1
+        L = self._lib
+        with torch.cuda.device(self.device):
+            L.check(L.lib().fp4t_allreduce_sum_bf16_multimem(
+                int(self._handle.multicast_ptr), self._flag_ptrs, self.rank, self.world, self.numel,
+                self._epoch, self.ctas, L.ptr(status) if status is not None else None,
+                L.stream_ptr(self.device)), "fp4t_allreduce_sum_bf16_multimem")

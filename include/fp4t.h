@@ -257,6 +257,27 @@ FP4T_API int fp4t_swizzle_colwise(const void* logical, void* dst, int64_t inner,
 FP4T_API int fp4t_unswizzle_colwise_to_rowwise(const void* src, void* dst, int64_t inner, int64_t outer,
                                       fp4t_stream_t stream);
 
+/*
+ * Data-parallel exchange of the weight gradients (in the reference: torch DDP's NCCL all-reduce
+ * of weight.grad / bias.grad after custom/linear/nvfp4.py:88-90).  In-place SUM all-reduce of a
+ * bf16 buffer over the `world` GPUs of one NVSwitch domain, reduced inside the switch:
+ *   multicast_ptr  multicast address of the buffer; every rank allocated it symmetrically and
+ *                  bound it to one NVLink multicast object (e.g. torch symmetric memory)
+ *   flag_ptrs      host array of `world` device pointers: rank r's flag array as mapped into
+ *                  this process, FP4T_ALLREDUCE_FLAG_WORDS 32-bit words each, zero before the
+ *                  first call and owned by this function afterwards
+ *   epoch          1, 2, 3, ... : the same value on every rank for the same call
+ *   ctas           upper bound on CTAs (the same on every rank); the kernel is small enough
+ *                  (256 threads, 40 registers) to be resident beside the persistent kernels
+ * Every rank must make the call; stream-ordered after the producer of the buffer.  A wait on a
+ * peer that runs out (2 s) writes 41 / 42 into `status` and ends the kernel.
+ */
+#define FP4T_ALLREDUCE_MAX_CTAS 256
+#define FP4T_ALLREDUCE_FLAG_WORDS (FP4T_ALLREDUCE_MAX_CTAS * 8)
+FP4T_API int fp4t_allreduce_sum_bf16_multimem(void* multicast_ptr, const void* const* flag_ptrs, int rank, int world,
+                                     int64_t numel, uint32_t epoch, int ctas, int32_t* status,
+                                     fp4t_stream_t stream);
+
 /* Byte-matrix transpose [rows, cols] -> [cols, rows] (E4M3 codes for the NN / NT operand
  * forms of custom/backend/csrc/cublaslt_mm_mxfp8.cu:70-88). */
 FP4T_API int fp4t_transpose_bytes(const void* src, void* dst, int64_t rows, int64_t cols,
