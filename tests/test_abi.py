@@ -43,3 +43,24 @@ def test_argument_errors_need_no_gpu():
     assert rc == -1 and b"null pointer" in L.fp4t_last_error()
     with pytest.raises(ValueError):
         _lib.check(rc, "fp4t_gemm_nvfp4")
+
+
+def test_allreduce_argument_errors_need_no_gpu():
+    """The in-switch all-reduce rejects bad world sizes, ranks, lengths and epochs before it
+    touches the device."""
+    from backend import _lib
+    L = _lib.lib()
+    buf = ctypes.c_void_p(0x1000)
+    flags = (ctypes.c_void_p * 8)(*[0x2000 + 0x100 * i for i in range(8)])
+
+    def call(world=2, rank=0, numel=64, epoch=1, ctas=16, ptr=buf, fl=flags):
+        return L.fp4t_allreduce_sum_bf16_multimem(ptr, fl, rank, world, numel, epoch, ctas, None, None)
+
+    assert call(world=9) == -1 and b"world size" in L.fp4t_last_error()
+    assert call(rank=2) == -1 and b"rank" in L.fp4t_last_error()
+    assert call(numel=12) == -1 and b"multiple of 8" in L.fp4t_last_error()
+    assert call(epoch=0) == -1 and b"epoch" in L.fp4t_last_error()
+    assert call(ctas=0) == -1 and b"ctas" in L.fp4t_last_error()
+    assert call(ptr=None) == -1 and b"null pointer" in L.fp4t_last_error()
+    assert call(ptr=ctypes.c_void_p(0x1008)) == -1 and b"aligned" in L.fp4t_last_error()
+    assert call(numel=0) == 0          # nothing to do, nothing launched

@@ -191,3 +191,32 @@ def test_chained_layer_calls_are_deterministic(ops, fmt):
             for a, b in zip(cur, ref):
                 assert torch.equal(a, b)
     ops.check_status()
+
+
+def test_layer_chain_replays_from_a_cuda_graph(ops):
+    """Quantizer and GEMM launches captured into a CUDA graph (static tile order inside a capture,
+    dependent-launch attribute kept) replay to the same bits as the eager launches."""
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    a = torch.randn(2048, 1024, device="cuda", generator=gen).to(torch.bfloat16)
+    b = torch.randn(1536, 1024, device="cuda", generator=gen).to(torch.bfloat16)
+    ac, asf, _, _ = ops.quantize_nvfp4(a, True, False)
+    bc, bsf, _, _ = ops.quantize_nvfp4(b, True, False)
+    want = ops.gemm_nvfp4(ac, asf, bc, bsf, None, torch.bfloat16).clone()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    out = torch.empty_like(want)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        for _ in range(2):      # warm-up on the capture stream
+            c2, s2, _, _ = ops.quantize_nvfp4(a, True, False)
+            ops.gemm_nvfp4(c2, s2, bc, bsf, None, torch.bfloat16, out=out)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            c2, s2, _, _ = ops.quantize_nvfp4(a, True, False)
+            ops.gemm_nvfp4(c2, s2, bc, bsf, None, torch.bfloat16, out=out)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    ops.check_status()
