@@ -38,7 +38,9 @@ def _worker(rank, world, port, q):
         nn.functional.mse_loss(model(xs), ys).backward()
         reducer.finish()
         out.append([p.grad.clone() for p in model.parameters()])
-    q.put((rank, [p.detach().clone() for p in model.parameters()], out[-1]))
+    # numpy arrays travel by value; tensors would be handed over through the sender's descriptor
+    # server, which is gone if this process exits before the parent has read the queue
+    q.put((rank, [p.detach().numpy().copy() for p in model.parameters()], [t.numpy().copy() for t in out[-1]]))
     dist.destroy_process_group()
 
 
@@ -53,7 +55,8 @@ def test_two_rank_gradient_average_matches_full_batch():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    (_, w0, g0), (_, w1, g1) = results
+    (_, w0, g0), (_, w1, g1) = [(r, [torch.from_numpy(a) for a in w], [torch.from_numpy(a) for a in g])
+                                for r, w, g in results]
     for a, b in zip(w0, w1):
         assert torch.equal(a, b)
     for a, b in zip(g0, g1):
