@@ -561,6 +561,16 @@ __global__ void colsum_generic_kernel(const TIn* __restrict__ x, int64_t rows, i
   colsum[c] += acc;
 }
 
+// Zeroes the column-sum scratch.  A kernel rather than a memset so that it sits in the chain of
+// dependent launches: a memset between two kernels makes the second wait for a full stream
+// serialisation instead of starting under the first one's tail.
+__global__ void zero_f32_kernel(float* __restrict__ p, int64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = 0.0f;
+}
+
 // fp32 accumulator -> bias gradient in the caller's dtype.
 __global__ void colsum_finalize_kernel(const float* __restrict__ colsum, void* __restrict__ out, int out_f32,
                                        int64_t cols) {
@@ -690,7 +700,17 @@ int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64
   FP4T_REQUIRE(bias_grad_dtype == FP4T_DT_BF16 || bias_grad_dtype == FP4T_DT_F32, "%s: bad bias_grad dtype", name);
   FP4T_REQUIRE(cols >= 0, "%s: negative cols", name);
   if (cols == 0) return FP4T_OK;
-  FP4T_CUDA(cudaMemsetAsync(colsum_scratch, 0, (size_t)cols * sizeof(float), stream));
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ceil_div(cols, 256), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    pdl_attribute(&attr);
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    FP4T_CUDA(cudaLaunchKernelEx(&cfg, zero_f32_kernel, colsum_scratch, cols));
+  }
   if (rows > 0) {
     const int rc = quantize_dispatch<kFmt>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise,
                                            noise_t, seed, colsum_scratch, stream);
