@@ -562,7 +562,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 // cluster-scope release): an arrive with .release.cluster from the second CTA every stage
 // cost about 1 us per stage.
 //   Warp roles per CTA: 0 operand producer, 1 MMA issuer (leader only), 2 tensor-memory
-// allocation, 3 scale-tile producer, 4-7 epilogue, 8-11 scale factors.  Operands and scale
+// allocation and then the tile scheduler (leader only: tile indices from the stream's device
+// counter, or the static order, published to both CTAs through a small queue), 3 scale-tile
+// producer, 4-7 epilogue, 8-11 scale factors.  Operands and scale
 // tiles have separate shared-memory rings (a scale slot is free once its bytes sit in the
 // scale warps' registers), and the epilogue leaves through swizzled staging tiles and tiled
 // TMA stores (clipped at the matrix edges); an output whose base or pitch is not 16-byte
