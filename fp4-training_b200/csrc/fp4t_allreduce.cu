@@ -18,8 +18,8 @@
 // which writes them into every rank's buffer; a second barrier makes the sums visible
 // everywhere before the kernel ends.  The barriers are per CTA (CTA b of every rank meets CTA b
 // of the others), flags live in a symmetric buffer of each rank and carry an increasing epoch,
-// so nothing has to be reset between calls.  Every wait is bounded (2 s) and reports through
-// the status word.
+// so nothing has to be reset between calls.  Every wait is bounded (half of the library's wait
+// limit: 2 s by default) and reports through the status word.
 #include "fp4t_common.cuh"
 #include "fp4t_ptx.cuh"
 
@@ -29,7 +29,6 @@ namespace {
 constexpr int kArThreads = 256;
 constexpr int kArMaxWorld = 8;
 constexpr int kArUnroll = 4;
-constexpr uint64_t kArTimeoutNs = 2000000000ull;
 
 struct ArParams {
   uint8_t* mc;                    // multicast address of the gradient buffer
@@ -76,10 +75,11 @@ allreduce_multimem_kernel(const ArParams p) {
       st_release_sys(p.flags[t] + (size_t)b * p.world + p.rank, target);
       const uint32_t* mine = p.flags[p.rank] + (size_t)b * p.world + t;
       const uint64_t t0 = globaltimer_ns();
+      const uint64_t limit = g_wait_timeout_ns >> 1;
       uint32_t spins = 0;
       while ((int32_t)(ld_acquire_sys(mine) - target) < 0) {
         __nanosleep(400);   // a warp that polls flat out takes issue slots from the compute kernel beside it
-        if ((++spins & 255u) == 0u && globaltimer_ns() - t0 > kArTimeoutNs) {
+        if ((++spins & 255u) == 0u && globaltimer_ns() - t0 > limit) {
           if (p.status) atomicCAS(p.status, 0, code);
           s_abort = 1;
           break;
@@ -112,6 +112,8 @@ allreduce_multimem_kernel(const ArParams p) {
 }
 
 }  // namespace
+
+FP4T_DEFINE_WAIT_TIMEOUT_SETTER(set_wait_timeout_allreduce)
 }  // namespace fp4t
 
 extern "C" int fp4t_allreduce_sum_bf16_multimem(void* multicast_ptr, const void* const* flag_ptrs, int rank, int world,

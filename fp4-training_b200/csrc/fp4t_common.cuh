@@ -53,6 +53,9 @@ inline void pdl_attribute(cudaLaunchAttribute* attr) {
   attr->val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
 }
 int reset_gemm_tile_counters(cudaStream_t stream);      // fp4t_gemm.cu
+int set_wait_timeout_gemm(uint64_t ns);                 // fp4t_gemm.cu
+int set_wait_timeout_quantize(uint64_t ns);             // fp4t_quantize.cu
+int set_wait_timeout_allreduce(uint64_t ns);            // fp4t_allreduce.cu
 int reset_quantize_tile_counters(cudaStream_t stream);  // fp4t_quantize.cu
 
 // 2-D tiled tensor map over a row-major matrix [outer, inner] of `dtype` elements whose rows

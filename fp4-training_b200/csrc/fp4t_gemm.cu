@@ -1241,6 +1241,8 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
 
 }  // namespace
 
+FP4T_DEFINE_WAIT_TIMEOUT_SETTER(set_wait_timeout_gemm)
+
 int reset_gemm_tile_counters(cudaStream_t stream) {
   void* addr = nullptr;
   FP4T_CUDA(cudaGetSymbolAddress(&addr, g_gemm_sched));

@@ -210,6 +210,14 @@ extern "C" int fp4t_reset_tile_counters(fp4t_stream_t stream) {
   return fp4t::reset_quantize_tile_counters(reinterpret_cast<cudaStream_t>(stream));
 }
 
+extern "C" int fp4t_set_wait_timeout_ns(uint64_t ns) {
+  FP4T_REQUIRE(ns >= 1000ull, "fp4t_set_wait_timeout_ns: the limit must be at least 1000 ns");
+  int rc = fp4t::set_wait_timeout_gemm(ns);
+  if (rc == FP4T_OK) rc = fp4t::set_wait_timeout_quantize(ns);
+  if (rc == FP4T_OK) rc = fp4t::set_wait_timeout_allreduce(ns);
+  return rc;
+}
+
 extern "C" int fp4t_set_sm_limit(int sms) {
   FP4T_REQUIRE(sms >= 0, "fp4t_set_sm_limit: negative limit");
   fp4t::g_sm_limit.store(sms, std::memory_order_relaxed);

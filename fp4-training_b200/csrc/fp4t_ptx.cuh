@@ -7,7 +7,17 @@
 
 namespace fp4t {
 
-constexpr uint64_t kWaitTimeoutNs = 4000000000ull;  // 4 s per wait
+constexpr uint64_t kWaitTimeoutNs = 4000000000ull;  // 4 s per wait (default)
+
+// Limit of every bounded wait, in nanoseconds.  One copy per translation unit (the library is
+// built without relocatable device code); fp4t_set_wait_timeout_ns updates all of them on the
+// current device.  Read only on the slow path of a wait.
+static __device__ uint64_t g_wait_timeout_ns = kWaitTimeoutNs;
+#define FP4T_DEFINE_WAIT_TIMEOUT_SETTER(fn_name)                                        \
+  int fn_name(uint64_t ns) {                                                            \
+    FP4T_CUDA(cudaMemcpyToSymbol(g_wait_timeout_ns, &ns, sizeof(ns), 0, cudaMemcpyHostToDevice)); \
+    return FP4T_OK;                                                                     \
+  }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -41,11 +51,12 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int32_t* status, int code) {
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = g_wait_timeout_ns;
   uint32_t spins = 0;
   while (!mbar_try(bar, parity)) {
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      if (globaltimer_ns() - t0 > limit) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -76,11 +87,12 @@ __device__ __forceinline__ uint32_t mbar_try_cluster(uint32_t bar, uint32_t pari
 static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                       int32_t* status, int code) {
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = g_wait_timeout_ns;
   uint32_t spins = 0;
   while (!mbar_try_cluster(bar, parity)) {
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      if (globaltimer_ns() - t0 > limit) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;

@@ -733,6 +733,8 @@ int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64
 
 }  // namespace
 
+FP4T_DEFINE_WAIT_TIMEOUT_SETTER(set_wait_timeout_quantize)
+
 int reset_quantize_tile_counters(cudaStream_t stream) {
   void* addr = nullptr;
   FP4T_CUDA(cudaGetSymbolAddress(&addr, g_quant_sched));

@@ -92,7 +92,10 @@ def quantize_nvfp4(tensor, rowwise=True, simulated=True, stochastic_rounding=Fal
     q = _ops.unpack_e2m1(codes)
     scales = unswizzle_rowwise(sf, src.shape[0], src.shape[1] // 16).view(torch.float8_e4m3fn)
     if simulated:
-        out = q * scales.to(torch.float32).repeat_interleave(16, dim=1)
+        # the reference multiplies by the fp32 scale BEFORE its rounding to E4M3
+        # (custom/quantize.py:75-76,96-97): recompute it from the block maxima
+        s32 = (src.reshape(src.shape[0], -1, 16).abs().amax(dim=-1) / E2M1_NORM_MAX).clamp(E4M3_SUBNORM_MIN, E4M3_NORM_MAX)
+        out = q * s32.repeat_interleave(16, dim=1)
         return out if rowwise else out.T
     scales = scales.squeeze()
     if rowwise:

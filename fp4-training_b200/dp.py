@@ -16,6 +16,7 @@ enough to be resident beside the persistent quantizers and GEMMs it overlaps wit
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 
 import torch
@@ -32,11 +33,21 @@ class _Bucket:
         for p in params:
             self.views.append(self.flat[off:off + p.numel()].view_as(p))
             off += p.numel()
-        self.pending = len(params)
+        self.fired = [False] * len(params)
         self.work = None
 
 
 class GradAllReducer:
+    """Bucketed, overlapped all-reduce (average) of parameter gradients.
+
+    One `finish()` per optimizer step.  With gradient accumulation, run all but the last
+    backward of a step inside `no_sync()`: hooks then leave the buckets alone and the last
+    backward's hooks reduce the accumulated `.grad`.  A backward outside `no_sync()` after a
+    bucket's collective has already started (a second backward without `finish()` in between)
+    is handled too: the running collective is waited for and the bucket is reduced again from
+    the up-to-date `.grad` in `finish()`.
+    """
+
     def __init__(self, params, process_group=None, bucket_bytes: int = 4 << 20):
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -55,18 +66,35 @@ class GradAllReducer:
             self.buckets.append(_Bucket(cur))
         self._index = {}
         self._handles = []
+        self._sync = True
         for b in self.buckets:
             for i, p in enumerate(b.params):
                 self._index[p] = (b, i)
                 self._handles.append(p.register_post_accumulate_grad_hook(self._on_grad))
 
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backward passes inside this context only accumulate into `.grad`."""
+        old, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = old
+
     def _on_grad(self, p):
-        if self.world == 1:
+        if self.world == 1 or not self._sync:
             return
         b, i = self._index[p]
+        if b.work is not None:
+            # this bucket's collective is already in flight and its gradient changed again:
+            # let it finish before the buffer is touched, and reduce afresh in finish()
+            b.work.wait()
+            b.work = None
+            b.fired = [False] * len(b.params)
+            return
         b.views[i].copy_(p.grad)
-        b.pending -= 1
-        if b.pending == 0:
+        b.fired[i] = True
+        if all(b.fired):
             b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
 
     def finish(self):
@@ -74,11 +102,14 @@ class GradAllReducer:
         if self.world == 1:
             return
         for b in self.buckets:
-            if b.pending != 0:
-                # a parameter received no gradient this step: reduce what there is
+            if b.work is None:
+                # not every hook fired (unused parameter, accumulation, a repeated backward):
+                # take each gradient as it stands now, zeros where there is none
                 for i, p in enumerate(b.params):
                     if p.grad is None:
                         b.views[i].zero_()
+                    else:
+                        b.views[i].copy_(p.grad)
                 b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
             b.work.wait()
             b.flat.div_(self.world)
@@ -87,7 +118,7 @@ class GradAllReducer:
                     p.grad = v.clone()
                 else:
                     p.grad.copy_(v)
-            b.pending = len(b.params)
+            b.fired = [False] * len(b.params)
             b.work = None
 
     def remove(self):

@@ -5,7 +5,8 @@
  *   - takes DEVICE pointers owned by the caller (unless a parameter says "host"),
  *   - enqueues its kernels on the given CUDA stream and returns without
  *     synchronising,
- *   - allocates nothing, creates no stream and keeps no reference to caller memory,
+ *   - allocates nothing, creates no stream and keeps no reference to caller memory
+ *     (one exception: fp4t_set_status_word stores the pointer it is given until it is replaced),
  *   - returns FP4T_OK (0) or a negative FP4T_ERR_* code; the text of the last
  *     error on the calling thread is available from fp4t_last_error().
  *
@@ -70,6 +71,16 @@ FP4T_API int fp4t_version(void);
  * memory and zeroes it.
  */
 FP4T_API int fp4t_set_status_word(int32_t* device_word);
+
+/*
+ * Every spin in the kernels (on an mbarrier, on a peer GPU's flag) is bounded: when the limit
+ * runs out the kernel writes a role code into the status word, lets its copies in flight land,
+ * frees its tensor memory and returns, so the context stays usable.  This sets the limit, in
+ * nanoseconds, for kernels launched afterwards on the CURRENT device (default 4 s; the peer
+ * waits of the all-reduce use half of it).  A synchronising set-up call.  No counterpart in
+ * the reference (cuBLASLt and NCCL have their own watchdogs).
+ */
+FP4T_API int fp4t_set_wait_timeout_ns(uint64_t ns);
 
 /*
  * Process-wide cap on the number of SMs the persistent kernels fill (0 = all).  A data-parallel

@@ -2,7 +2,8 @@
 
 Run once, in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py [--reference /path/to/fp4-training]
+    python tests/golden/make_golden.py --reference /path/to/fp4-training
+    (or FP4T_REFERENCE=/path/to/fp4-training python tests/golden/make_golden.py)
 
 It imports the reference's custom/swizzle.py and custom/quantize.py by file
 path (the NVFP4 quantizer and both swizzles are pure PyTorch and run on CPU),
@@ -14,6 +15,10 @@ of the MXFP8 path is executed.  The outputs are small .npz files:
                         scale bytes (logical and swizzled), for the
                         deterministic and the stochastic path (noise stored)
   swizzle_*.npz         scale matrices and both reference swizzles
+  nvfp4_api_*.npz       what the reference's public entry points return, call by call:
+                        quantize_nvfp4(rowwise in {True, False}, simulated in {True, False}),
+                        q_nvfp4_rowwise / q_nvfp4_colwise with and without stochastic
+                        rounding (the noise the reference drew is stored)
 
 The GPU box has no reference checkout; tests read only these fixtures there.
 """
@@ -29,11 +34,14 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REFERENCE = os.environ.get("FP4T_REFERENCE", "/root/reference")
+DEFAULT_REFERENCE = os.environ.get("FP4T_REFERENCE", "")
 
 
 def load_reference(ref_root: str = DEFAULT_REFERENCE):
-    """Return (quantize_module, swizzle_module) of the reference, or None if absent."""
+    """Return (quantize_module, swizzle_module) of the reference checkout at `ref_root`
+    (argument, or the FP4T_REFERENCE environment variable), or None if there is none."""
+    if not ref_root:
+        return None
     qpath = os.path.join(ref_root, "custom", "quantize.py")
     spath = os.path.join(ref_root, "custom", "swizzle.py")
     if not (os.path.isfile(qpath) and os.path.isfile(spath)):
@@ -104,6 +112,9 @@ CASES = [
     ("grad", 50 * 2, 48, 9),
 ]
 
+# cases for the public entry points (rows and cols multiples of 16, at least two blocks each way)
+API_CASES = [("normal", 64, 128, 11), ("outlier", 32, 512, 12), ("grad", 48, 80, 13), ("weight", 96, 192, 14)]
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -138,6 +149,29 @@ def main():
             out["codes_t"] = reference_pack(qt).numpy()
             out["scale_swizzled_t"] = st.numpy()
         np.savez_compressed(os.path.join(HERE, f"nvfp4_rowwise_{kind}_{rows}x{cols}.npz"), **out)
+
+    for kind, rows, cols, seed in API_CASES:
+        x = _inputs(kind, rows, cols, seed)
+        out = {"x_bits": x.view(torch.int16).numpy()}
+        for rowwise in (True, False):
+            tag = "row" if rowwise else "col"
+            out[f"sim_{tag}"] = rq.quantize_nvfp4(x, rowwise=rowwise, simulated=True).contiguous().numpy()
+            q, s = rq.quantize_nvfp4(x, rowwise=rowwise, simulated=False)
+            out[f"q_{tag}"] = q.contiguous().numpy()
+            out[f"s_{tag}"] = s.contiguous().view(torch.uint8).numpy()
+            fn = rq.q_nvfp4_rowwise if rowwise else rq.q_nvfp4_colwise
+            qv, sw_ = fn(x)
+            assert torch.equal(qv, q.contiguous())
+            out[f"sw_{tag}"] = sw_.contiguous().numpy()
+            # stochastic rounding: the reference draws rand_like on the blocked (possibly transposed) tensor
+            torch.manual_seed(2000 + seed)
+            qs, ss = fn(x, sr=True)
+            torch.manual_seed(2000 + seed)
+            u = torch.rand(rows, cols // 16, 16) if rowwise else torch.rand(cols, rows // 16, 16)
+            out[f"sr_noise_{tag}"] = u.numpy()
+            out[f"sr_q_{tag}"] = qs.numpy()
+            assert torch.equal(ss, sw_)
+        np.savez_compressed(os.path.join(HERE, f"nvfp4_api_{kind}_{rows}x{cols}.npz"), **out)
 
     g = torch.Generator().manual_seed(99)
     sw = {}

@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_reference_arm_prints_one_contract_line():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
-                          "--warmup", "1"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+                          "--warmup", "1", "--sample-rows", "256"], capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["n_gpus"] == 1 and line["higher_is_better"] is True
@@ -19,3 +19,15 @@ def test_reference_arm_prints_one_contract_line():
     assert line["cpu_baseline"]["value"] == line["value"] == line["e2e"]["value"]
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert line["gpu_launches"] == 0 and "workload" in line["config"]
+    assert line["steps"] == 1 and line["warmup"] == 1
+    # both arms print the same `config` object for the default workload
+    sys.path.insert(0, ROOT)
+    import bench
+    assert line["config"] == bench.base_config(1)
+
+
+def test_config1_cpu_baseline_runs_and_reports_cores():
+    sys.path.insert(0, ROOT)
+    import bench
+    r = bench.cpu_config1_baseline(reps=3)
+    assert r["value"] > 0 and r["cores"] >= 1 and r["runs"] == 3 and "512" in r["workload"]

@@ -73,6 +73,78 @@ def test_two_rank_gradient_average_matches_full_batch():
         assert torch.allclose(p.grad, got, atol=1e-6)
 
 
+def _accum_worker(rank, world, port, q):
+    """Gradient accumulation (two backwards per step, with and without no_sync) and a parameter
+    that takes no part in the loss while its .grad tensor persists between steps."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "fp4-training_b200"))
+    from dp import GradAllReducer, broadcast_parameters
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.manual_seed(7)
+    model = nn.Sequential(nn.Linear(16, 32), nn.GELU(), nn.Linear(32, 8))
+    unused = nn.Linear(8, 8)
+    broadcast_parameters(model)
+    params = list(model.parameters()) + list(unused.parameters())
+    reducer = GradAllReducer(params, bucket_bytes=1024)
+    g = torch.Generator().manual_seed(5)
+    x_all, y_all = torch.randn(16, 16, generator=g), torch.randn(16, 8, generator=g)
+    # rank r owns micro-batches 2r and 2r+1 (4 samples each)
+    mb = [(x_all[i * 4:(i + 1) * 4], y_all[i * 4:(i + 1) * 4]) for i in range(4)]
+    mine = mb[2 * rank:2 * rank + 2]
+    res = {}
+    for mode in ("no_sync", "plain"):
+        for step in range(2):
+            for p in params:
+                if p.grad is not None:
+                    p.grad.zero_()                      # set_to_none=False style: stale tensors stay
+            if step == 0:
+                # give the unused layer a stale nonzero gradient that must NOT be averaged back in
+                for p in unused.parameters():
+                    p.grad = torch.full_like(p, 3.0)
+                    p.grad.zero_()
+            if mode == "no_sync":
+                with reducer.no_sync():
+                    nn.functional.mse_loss(model(mine[0][0]), mine[0][1]).backward()
+                nn.functional.mse_loss(model(mine[1][0]), mine[1][1]).backward()
+            else:
+                nn.functional.mse_loss(model(mine[0][0]), mine[0][1]).backward()
+                nn.functional.mse_loss(model(mine[1][0]), mine[1][1]).backward()
+            reducer.finish()
+        res[mode] = [p.grad.clone().numpy().copy() for p in params]
+    q.put((rank, res))
+    dist.destroy_process_group()
+
+
+def test_accumulation_and_unused_parameters():
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_accum_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # reference: sum over the four micro-batch mean losses, divided by the 2 ranks
+    torch.manual_seed(7)
+    model = nn.Sequential(nn.Linear(16, 32), nn.GELU(), nn.Linear(32, 8))
+    g = torch.Generator().manual_seed(5)
+    x_all, y_all = torch.randn(16, 16, generator=g), torch.randn(16, 8, generator=g)
+    for i in range(4):
+        nn.functional.mse_loss(model(x_all[i * 4:(i + 1) * 4]), y_all[i * 4:(i + 1) * 4]).backward()
+    want = [p.grad / 2 for p in model.parameters()]
+    for mode in ("no_sync", "plain"):
+        for rank in (0, 1):
+            got = [torch.from_numpy(a) for a in results[rank][mode]]
+            for w, gt in zip(want, got[:len(want)]):
+                assert torch.allclose(w, gt, atol=1e-6), f"{mode}: rank {rank} gradient differs from the full-batch one"
+            for gt in got[len(want):]:
+                assert float(gt.abs().max()) == 0.0, f"{mode}: an unused parameter received a gradient"
+
+
 def _lonely_worker(port, q):
     """Rank 0 of a 2-rank job whose rank 1 never starts."""
     import datetime

@@ -1,11 +1,8 @@
 """Full-size cases of the benchmark configurations, checked through properties that do not
 need a CPU pass over the whole tensor:
 
-  * the transposed output of one fused launch is bit-identical to a row-wise launch on the
-    materialised transpose (two different code paths of the kernel),
-  * scale bytes are the E4M3 / E8M0 encodings of the block amax rule, recomputed with torch
-    on the GPU from the oracle's formulas,
-  * dequantized codes stay within half a grid step of the input,
+  * NVFP4 codes and scale bytes of the benchmark tensors are compared byte for byte with the
+    oracle's quantizer evaluated on the same (GPU-resident) tensors,
   * GEMM outputs match an fp32 matmul of the dequantized operands (oracle dequantizers run
     on the GPU tensors), rel-Frobenius <= 1e-2 for bf16 output.
 """
@@ -36,23 +33,50 @@ def _unswz(sf, outer, inner):
     return orc.unswizzle_rowwise(sf.cpu(), outer, inner).cuda()
 
 
-def test_nvfp4_quantizer_config2_properties(ops):
-    x, _, _ = _inputs(8192, 4096, 4096, 0)
-    codes, sf, codes_t, sf_t = ops.quantize_nvfp4(x, True, True)
-    # transposed output == row-wise quantization of the materialised transpose
-    c2, s2, _, _ = ops.quantize_nvfp4(x.t().contiguous(), True, False)
-    assert torch.equal(codes_t, c2) and torch.equal(sf_t, s2)
-    # scale rule, recomputed with the oracle's formula on the GPU
-    want = orc.nvfp4_block_scales(x).to(torch.float8_e4m3fn).view(torch.uint8)
-    got = _unswz(sf, 8192, 256)
-    assert torch.equal(got, want)
-    # codes decode to within half a step of x / s (steps: 0.5 below 2, 1 below 4, 2 above)
-    s32 = orc.nvfp4_block_scales(x).repeat_interleave(16, dim=1)
-    y = x.float() / s32
-    q = orc.e2m1_decode(orc.unpack_fp4_pairs(codes))
-    step = torch.where(y.abs() < 2, 0.5, torch.where(y.abs() < 4, 1.0, 2.0))
-    assert bool(((q - y).abs() <= step / 2 + 1e-6).all())
-    assert bool((q.abs() <= 6).all())
+def _oracle_codes_and_scales(t, noise=None):
+    """The oracle's row-wise quantizer run on the GPU tensors (it is plain torch arithmetic,
+    IEEE divisions included): packed codes [R, C/2] and logical scale bytes [R, C/16]."""
+    codes, sb = orc.nvfp4_quantize_rowwise(t, noise)
+    return orc.pack_fp4_pairs(codes), sb
+
+
+def _count_diff(a, b):
+    return int((a != b).sum().item())
+
+
+def test_nvfp4_quantizer_config2_bit_exact(ops):
+    """Every code and every scale byte of the three tensors of the benchmark configuration
+    (X with its x50 outliers, W, dY with stochastic rounding on a given noise tensor), row-wise
+    and transposed, against the oracle on the same tensors: 0 differing bytes."""
+    n, ic, oc = 8192, 4096, 4096
+    x, w, g = _inputs(n, ic, oc, 0)
+    for name, t in (("X", x), ("W", w)):
+        r, c = t.shape
+        codes, sf, codes_t, sf_t = ops.quantize_nvfp4(t, True, True)
+        want_c, want_s = _oracle_codes_and_scales(t)
+        assert _count_diff(codes, want_c) == 0, f"{name}: row-wise codes"
+        assert _count_diff(_unswz(sf, r, c // 16), want_s) == 0, f"{name}: row-wise scales"
+        del want_c, want_s
+        want_c, want_s = _oracle_codes_and_scales(t.t().contiguous())
+        assert _count_diff(codes_t, want_c) == 0, f"{name}: transposed codes"
+        assert _count_diff(_unswz(sf_t, c, r // 16), want_s) == 0, f"{name}: transposed scales"
+        del want_c, want_s, codes, codes_t
+    # dY: stochastic rounding with explicit noise (one tensor per emitted copy, as the reference
+    # draws one per quantizer call)
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    u = torch.rand(n, oc, device="cuda", generator=gen)
+    ut = torch.rand(oc, n, device="cuda", generator=gen)
+    codes, sf, codes_t, sf_t = ops.quantize_nvfp4(g, True, True, sr=ops.SR_NOISE, noise=u, noise_t=ut)
+    want_c, want_s = _oracle_codes_and_scales(g, u)
+    assert _count_diff(codes, want_c) == 0, "dY: row-wise SR codes"
+    assert _count_diff(_unswz(sf, n, oc // 16), want_s) == 0, "dY: row-wise scales"
+    del want_c, want_s
+    want_c, want_s = _oracle_codes_and_scales(g.t().contiguous(), ut)
+    assert _count_diff(codes_t, want_c) == 0, "dY: transposed SR codes"
+    assert _count_diff(_unswz(sf_t, oc, n // 16), want_s) == 0, "dY: transposed scales"
+    # padding bytes of the scale buffers are zero (they are read by the GEMM's K tail handling)
+    assert int(sf.sum().item()) == int(_unswz(sf, n, oc // 16).sum().item())
+    ops.check_status()
 
 
 def test_nvfp4_linear_config2_against_dequantized_matmul(ops):
@@ -106,6 +130,50 @@ def test_mxfp8_mlp_pair_config3_against_dequantized_matmul(ops):
     out = ops.gemm_mxfp8(hc, hsf, dc, dsf, None, torch.bfloat16)
     ref = deq(hc, hsf, n, hid) @ deq(dc, dsf, ic, hid).t()
     assert orc.rel_frobenius(out.float(), ref) <= 1e-2
+    ops.check_status()
+
+
+def test_mxfp8_mlp_pair_config3_backward_gemms(ops):
+    """dgrad and wgrad of both projections of the MXFP8 MLP configuration at full size
+    (N=16384, 4096 -> 14336 -> 4096), each against the fp32 matmul of its dequantized operands.
+    Operand forms follow the reference's backward (custom/linear/mxfp8.py:60-80): dY row-wise
+    for dgrad, the column-wise (here: transposed) copies of W, X and dY for the rest."""
+    n, ic, hid = 16384, 4096, 14336
+    g = torch.Generator(device="cuda").manual_seed(3)
+    chan = torch.distributions.StudentT(3.0).sample((ic,)).abs().cuda()
+    x = (torch.randn(n, ic, device="cuda", generator=g) * chan).to(torch.bfloat16)
+    w_up = (torch.randn(hid, ic, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    w_dn = (torch.randn(ic, hid, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    gy = (torch.randn(n, ic, device="cuda", generator=g) * 1e-3).to(torch.bfloat16)
+
+    def deq(c, s, outer, k):
+        return orc.mxfp8_dequant(c, _unswz(s, outer, k // 32))
+
+    def check(pc, ps, qc, qs, rows, cols, k, what):
+        out = ops.gemm_mxfp8(pc, ps, qc, qs, None, torch.bfloat16)
+        ref = deq(pc, ps, rows, k) @ deq(qc, qs, cols, k).t()
+        err = orc.rel_frobenius(out.float(), ref)
+        assert err <= 1e-2, f"{what}: rel-Frobenius {err:.3e}"
+        return out
+
+    # forward intermediates needed by the backward operands
+    xc, xsf, xtc, xtsf = ops.quantize_mxfp8(x, True, True)
+    uc, usf, utc, utsf = ops.quantize_mxfp8(w_up, True, True)
+    h = ops.gemm_mxfp8(xc, xsf, uc, usf, None, torch.bfloat16)
+    del xc, xsf, uc, usf
+    _, _, htc, htsf = ops.quantize_mxfp8(h, False, True)
+    del h
+    _, _, dtc, dtsf = ops.quantize_mxfp8(w_dn, False, True)
+    # down-projection backward: dH = G W_dn, dW_dn = G^T H
+    gc, gsf, gtc, gtsf = ops.quantize_mxfp8(gy, True, True)
+    dh = check(gc, gsf, dtc, dtsf, n, hid, ic, "down-projection dgrad")
+    check(gtc, gtsf, htc, htsf, ic, hid, n, "down-projection wgrad")
+    del gc, gsf, gtc, gtsf, htc, htsf, dtc, dtsf
+    # up-projection backward: dX = dH W_up, dW_up = dH^T X
+    hc, hsf, hgt, hgtsf = ops.quantize_mxfp8(dh, True, True)
+    del dh
+    check(hc, hsf, utc, utsf, n, ic, hid, "up-projection dgrad")
+    check(hgt, hgtsf, xtc, xtsf, hid, ic, n, "up-projection wgrad")
     ops.check_status()
 
 
