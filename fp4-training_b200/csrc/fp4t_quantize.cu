@@ -130,71 +130,97 @@ __device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
   const uint8_t* src = c.tile + r_base * 256 + kb * (C::kBlk * 2);
   uint8_t* sf_dst = c.sf_row_s + (kb >> 2) * 512 + (kb & 3);
   const uint32_t seed_lo = (uint32_t)p.seed, seed_hi = (uint32_t)(p.seed >> 32);
+
+  // Phase 1: every load of the thread's kIts blocks is issued before any arithmetic, and every
+  // store comes after all of it.  A store into the scale staging area may alias the tile as
+  // far as the compiler can tell, so loads written after it would wait for it; separating the
+  // phases lets the shared-memory latency of all blocks overlap.
+  uint32_t w[kIts][kVecs][4];
 #pragma unroll
-  for (int it = 0; it < kIts; ++it, out += out_step) {
-    const int r = it * kRowsPerIt + r_base;
-    const int64_t gr = c.row0 + r;
-    uint32_t w[kVecs][4];
+  for (int it = 0; it < kIts; ++it) {
 #pragma unroll
     for (int v = 0; v < kVecs; ++v) {
       const uint4 q = *reinterpret_cast<const uint4*>(src + it * kRowsPerIt * 256 + v * 16);
-      w[v][0] = q.x; w[v][1] = q.y; w[v][2] = q.z; w[v][3] = q.w;
+      w[it][v][0] = q.x; w[it][v][1] = q.y; w[it][v][2] = q.z; w[it][v][3] = q.w;
     }
-    float amax = amax8(w[0]);
+  }
+  float amax[kIts];
 #pragma unroll
-    for (int v = 1; v < kVecs; ++v) amax = fmaxf(amax, amax8(w[v]));
-    const bool valid = !kEdge || (col_ok && gr < p.rows);
-    uint32_t sf_byte;
-    if (kFmt == kNvfp4) {
-      float s, rcp;
-      nvfp4_scale_from_table(c.scale_tab, amax, s, rcp);
-      const uint64_t rcp2 = pack2(rcp, rcp), neg2 = pack2(-s, -s);
-      uint32_t packed[2];
+  for (int it = 0; it < kIts; ++it) {
+    amax[it] = amax8(w[it][0]);
+#pragma unroll
+    for (int v = 1; v < kVecs; ++v) amax[it] = fmaxf(amax[it], amax8(w[it][v]));
+  }
+  bool valid[kIts];
+#pragma unroll
+  for (int it = 0; it < kIts; ++it) valid[it] = !kEdge || (col_ok && c.row0 + it * kRowsPerIt + r_base < p.rows);
+
+  uint32_t sf_byte[kIts];
+  if (kFmt == kNvfp4) {
+    float s[kIts], rcp[kIts];
+#pragma unroll
+    for (int it = 0; it < kIts; ++it) nvfp4_scale_from_table(c.scale_tab, amax[it], s[it], rcp[it]);
+    uint32_t packed[kIts][2];
+#pragma unroll
+    for (int it = 0; it < kIts; ++it) {
+      const int64_t gr = c.row0 + it * kRowsPerIt + r_base;
+      const uint64_t rcp2 = pack2(rcp[it], rcp[it]), neg2 = pack2(-s[it], -s[it]);
 #pragma unroll
       for (int v = 0; v < 2; ++v) {
         float y[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[v][j]), neg2, rcp2), y[2 * j], y[2 * j + 1]);
+        for (int j = 0; j < 4; ++j) unpack2(div_corrected2(bf16x2_to_f32x2(w[it][v][j]), neg2, rcp2), y[2 * j], y[2 * j + 1]);
         if (kSr == FP4T_SR_HASH) {
           uint32_t h1;
           const uint32_t h0 = hash_pair((uint32_t)((gr * p.cols + gc) >> 3) + v, seed_lo, seed_hi, h1);
-          packed[v] = cvt_rs_e2m1x4(y[0], y[1], y[2], y[3], h0) | (cvt_rs_e2m1x4(y[4], y[5], y[6], y[7], h1) << 16);
+          packed[it][v] = cvt_rs_e2m1x4(y[0], y[1], y[2], y[3], h0) | (cvt_rs_e2m1x4(y[4], y[5], y[6], y[7], h1) << 16);
         } else {
           if (kSr == FP4T_SR_NOISE) {
             const float4* np = reinterpret_cast<const float4*>(p.noise + gr * p.cols + gc + 8 * v);
-            const float4 n0 = valid ? __ldg(np) : make_float4(0.5f, 0.5f, 0.5f, 0.5f);
-            const float4 n1 = valid ? __ldg(np + 1) : make_float4(0.5f, 0.5f, 0.5f, 0.5f);
+            const float4 n0 = valid[it] ? __ldg(np) : make_float4(0.5f, 0.5f, 0.5f, 0.5f);
+            const float4 n1 = valid[it] ? __ldg(np + 1) : make_float4(0.5f, 0.5f, 0.5f, 0.5f);
             y[0] = sr_round(y[0], n0.x); y[1] = sr_round(y[1], n0.y); y[2] = sr_round(y[2], n0.z); y[3] = sr_round(y[3], n0.w);
             y[4] = sr_round(y[4], n1.x); y[5] = sr_round(y[5], n1.y); y[6] = sr_round(y[6], n1.z); y[7] = sr_round(y[7], n1.w);
           }
-          packed[v] = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
+          packed[it][v] = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
         }
       }
-      if (valid) *reinterpret_cast<uint2*>(out) = make_uint2(packed[0], packed[1]);
-      sf_byte = e4m3_byte_of_scale(s);
-    } else {
-      const uint32_t sb = mx_scale_byte(amax);
+      sf_byte[it] = e4m3_byte_of_scale(s[it]);
+    }
+#pragma unroll
+    for (int it = 0; it < kIts; ++it)
+      if (valid[it]) *reinterpret_cast<uint2*>(out + it * out_step) = make_uint2(packed[it][0], packed[it][1]);
+  } else {
+    uint32_t o[kIts][8];
+#pragma unroll
+    for (int it = 0; it < kIts; ++it) {
+      const uint32_t sb = mx_scale_byte(amax[it]);
       const float inv = mx_inv_scale(sb);
-      uint32_t o[8];
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint32_t w0 = w[v][2 * h], w1 = w[v][2 * h + 1];
-          o[2 * v + h] = mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 << 16), inv, 0.0f),
-                                            fmaf(__uint_as_float(w0 & 0xFFFF0000u), inv, 0.0f)) |
-                         (mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w1 << 16), inv, 0.0f),
-                                              fmaf(__uint_as_float(w1 & 0xFFFF0000u), inv, 0.0f)) << 16);
+          const uint32_t w0 = w[it][v][2 * h], w1 = w[it][v][2 * h + 1];
+          o[it][2 * v + h] = mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w0 << 16), inv, 0.0f),
+                                                fmaf(__uint_as_float(w0 & 0xFFFF0000u), inv, 0.0f)) |
+                             (mx_e4m3x2_from_bf16(fmaf(__uint_as_float(w1 << 16), inv, 0.0f),
+                                                  fmaf(__uint_as_float(w1 & 0xFFFF0000u), inv, 0.0f)) << 16);
         }
       }
-      if (valid) {
-        reinterpret_cast<uint4*>(out)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        reinterpret_cast<uint4*>(out)[1] = make_uint4(o[4], o[5], o[6], o[7]);
-      }
-      sf_byte = sb;
+      sf_byte[it] = sb;
     }
-    sf_dst[sf_tile_offset(r, 0)] = valid ? (uint8_t)sf_byte : (uint8_t)0;
+#pragma unroll
+    for (int it = 0; it < kIts; ++it) {
+      if (valid[it]) {
+        uint4* dst = reinterpret_cast<uint4*>(out + it * out_step);
+        dst[0] = make_uint4(o[it][0], o[it][1], o[it][2], o[it][3]);
+        dst[1] = make_uint4(o[it][4], o[it][5], o[it][6], o[it][7]);
+      }
+    }
   }
+#pragma unroll
+  for (int it = 0; it < kIts; ++it)
+    sf_dst[sf_tile_offset(it * kRowsPerIt + r_base, 0)] = valid[it] ? (uint8_t)sf_byte[it] : (uint8_t)0;
 }
 
 // ---- transposed pass: a thread handles 2 adjacent columns x 32 rows --------------------
@@ -206,34 +232,40 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
   const bool okA = rows_ok && (!kEdge || gcA < p.cols), okB = rows_ok && (!kEdge || gcA + 1 < p.cols);
   const uint32_t* col_words = reinterpret_cast<const uint32_t*>(c.tile + (q * 32) * 256) + cp;
   uint64_t sum2 = 0;   // packed fp32 (0, 0)
+  // all 32 words of the thread's two columns first (see row_pass on why loads precede stores)
+  uint32_t w[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) w[j] = col_words[j * 64];
   if (kFmt == kNvfp4) {
     uint32_t outA[4], outB[4];
+    uint32_t sfA[2], sfB[2];
     const uint32_t seed_lo = (uint32_t)p.seed ^ 0x5BD1E995u, seed_hi = (uint32_t)(p.seed >> 32);
+    float sA[2], sB[2], rA[2], rB[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      uint32_t w[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) w[j] = col_words[(h * 16 + j) * 64];
       float mA[4], mB[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        mA[j] = fmaxf(fmaxf(fabsf(__uint_as_float(w[4 * j] << 16)), fabsf(__uint_as_float(w[4 * j + 1] << 16))),
-                      fmaxf(fabsf(__uint_as_float(w[4 * j + 2] << 16)), fabsf(__uint_as_float(w[4 * j + 3] << 16))));
-        mB[j] = fmaxf(fmaxf(fabsf(__uint_as_float(w[4 * j] & 0xFFFF0000u)), fabsf(__uint_as_float(w[4 * j + 1] & 0xFFFF0000u))),
-                      fmaxf(fabsf(__uint_as_float(w[4 * j + 2] & 0xFFFF0000u)), fabsf(__uint_as_float(w[4 * j + 3] & 0xFFFF0000u))));
+        const uint32_t* ww = w + h * 16 + 4 * j;
+        mA[j] = fmaxf(fmaxf(fabsf(__uint_as_float(ww[0] << 16)), fabsf(__uint_as_float(ww[1] << 16))),
+                      fmaxf(fabsf(__uint_as_float(ww[2] << 16)), fabsf(__uint_as_float(ww[3] << 16))));
+        mB[j] = fmaxf(fmaxf(fabsf(__uint_as_float(ww[0] & 0xFFFF0000u)), fabsf(__uint_as_float(ww[1] & 0xFFFF0000u))),
+                      fmaxf(fabsf(__uint_as_float(ww[2] & 0xFFFF0000u)), fabsf(__uint_as_float(ww[3] & 0xFFFF0000u))));
       }
       const float amA = fmaxf(fmaxf(mA[0], mA[1]), fmaxf(mA[2], mA[3]));
       const float amB = fmaxf(fmaxf(mB[0], mB[1]), fmaxf(mB[2], mB[3]));
-      float sA, sB, rA, rB;
-      nvfp4_scale_from_table(c.scale_tab, amA, sA, rA);
-      nvfp4_scale_from_table(c.scale_tab, amB, sB, rB);
-      const uint64_t rcp2 = pack2(rA, rB), neg2 = pack2(-sA, -sB);
+      nvfp4_scale_from_table(c.scale_tab, amA, sA[h], rA[h]);
+      nvfp4_scale_from_table(c.scale_tab, amB, sB[h], rB[h]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint64_t rcp2 = pack2(rA[h], rB[h]), neg2 = pack2(-sA[h], -sB[h]);
 #pragma unroll
       for (int g8 = 0; g8 < 2; ++g8) {
         float yA[8], yB[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint64_t x2 = bf16x2_to_f32x2(w[g8 * 8 + j]);
+          const uint64_t x2 = bf16x2_to_f32x2(w[h * 16 + g8 * 8 + j]);
           if (kColsum) sum2 = add2(sum2, x2);
           unpack2(div_corrected2(x2, neg2, rcp2), yA[j], yB[j]);
         }
@@ -261,9 +293,8 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
         outA[2 * h + g8] = a8;
         outB[2 * h + g8] = b8;
       }
-      const int kb = q * 2 + h;
-      c.sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp, kb)] = okA ? (uint8_t)e4m3_byte_of_scale(sA) : (uint8_t)0;
-      c.sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp + 1, kb)] = okB ? (uint8_t)e4m3_byte_of_scale(sB) : (uint8_t)0;
+      sfA[h] = e4m3_byte_of_scale(sA[h]);
+      sfB[h] = e4m3_byte_of_scale(sB[h]);
     }
     if (okA)
       *reinterpret_cast<uint4*>(p.codes_t + gcA * (p.rows >> 1) + (gr0 >> 1)) =
@@ -271,10 +302,13 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
     if (okB)
       *reinterpret_cast<uint4*>(p.codes_t + (gcA + 1) * (p.rows >> 1) + (gr0 >> 1)) =
           make_uint4(outB[0], outB[1], outB[2], outB[3]);
-  } else {
-    uint32_t w[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) w[j] = col_words[j * 64];
+    for (int h = 0; h < 2; ++h) {
+      const int kb = q * 2 + h;
+      c.sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp, kb)] = okA ? (uint8_t)sfA[h] : (uint8_t)0;
+      c.sf_col_s[(kb >> 2) * 512 + sf_tile_offset(2 * cp + 1, kb)] = okB ? (uint8_t)sfB[h] : (uint8_t)0;
+    }
+  } else {
     float amA = 0.0f, amB = 0.0f;
 #pragma unroll
     for (int j = 0; j < 32; j += 2) {

@@ -87,20 +87,33 @@ def quantize_nvfp4(tensor, rowwise=True, simulated=True, stochastic_rounding=Fal
     if rowwise is False and r % 16 != 0:
         raise ValueError("For nvfp4 column-wise quantization, the number of rows must be a multiple of 16")
     src = tensor if rowwise else tensor.T.contiguous()
-    noise = torch.rand(src.shape[0], src.shape[1] // 16, 16, device=src.device) if stochastic_rounding else None
+    noise = _sr_noise(r, c, rowwise, tensor.device) if stochastic_rounding else None
     codes, sf, _, _ = nvfp4_fused(src, True, False, sr=stochastic_rounding, noise=noise)
     q = _ops.unpack_e2m1(codes)
     scales = unswizzle_rowwise(sf, src.shape[0], src.shape[1] // 16).view(torch.float8_e4m3fn)
     if simulated:
         # the reference multiplies by the fp32 scale BEFORE its rounding to E4M3
         # (custom/quantize.py:75-76,96-97): recompute it from the block maxima
-        s32 = (src.reshape(src.shape[0], -1, 16).abs().amax(dim=-1) / E2M1_NORM_MAX).clamp(E4M3_SUBNORM_MIN, E4M3_NORM_MAX)
+        amax = src.reshape(src.shape[0], -1, 16).abs().amax(dim=-1)
+        # a tensor divisor: on CUDA, division by a Python scalar becomes a multiply by 1/6
+        s32 = (amax / torch.full_like(amax, E2M1_NORM_MAX)).clamp(E4M3_SUBNORM_MIN, E4M3_NORM_MAX)
         out = q * s32.repeat_interleave(16, dim=1)
         return out if rowwise else out.T
     scales = scales.squeeze()
     if rowwise:
         return q, scales
     return q.T, scales.T
+
+
+def _sr_noise(r: int, c: int, rowwise: bool, device) -> torch.Tensor:
+    """Uniform noise for a [r, c] input in the order the reference consumes its generator
+    (custom/quantize.py:88): row-wise one draw per element of the blocked [r, c/16, 16] tensor;
+    column-wise the reference's blocked tensor is a strided view of the transposed input and
+    `rand_like` fills it in memory order, i.e. in the layout of the original [r, c] tensor.
+    Returned in the logical layout of the tensor that is quantized row-wise."""
+    if rowwise:
+        return torch.rand(r, c // 16, 16, device=device)
+    return torch.rand(r, c, device=device).T.contiguous()
 
 
 def unswizzle_rowwise(sf: torch.Tensor, outer: int, inner: int) -> torch.Tensor:
@@ -117,7 +130,7 @@ def q_nvfp4_rowwise(tensor, sr=False):
     _check_2d(tensor, "nvfp4")
     if tensor.shape[1] % 16 != 0:
         raise ValueError("For nvfp4 row-wise quantization, the number of columns must be a multiple of 16")
-    noise = torch.rand(tensor.shape[0], tensor.shape[1] // 16, 16, device=tensor.device) if sr else None
+    noise = _sr_noise(tensor.shape[0], tensor.shape[1], True, tensor.device) if sr else None
     codes, sf, _, _ = nvfp4_fused(tensor, True, False, sr=sr, noise=noise)
     return _ops.unpack_e2m1(codes), sf
 
@@ -129,7 +142,7 @@ def q_nvfp4_colwise(tensor, sr=False):
     if r % 16 != 0:
         raise ValueError("For nvfp4 column-wise quantization, the number of rows must be a multiple of 16")
     t = tensor.T.contiguous()
-    noise = torch.rand(c, r // 16, 16, device=tensor.device) if sr else None
+    noise = _sr_noise(r, c, False, tensor.device) if sr else None
     codes, sf, _, _ = nvfp4_fused(t, True, False, sr=sr, noise=noise)
     from .swizzle import swizzle_colwise_scale
     logical = unswizzle_rowwise(sf, c, r // 16)            # [C, R/16]

@@ -163,7 +163,9 @@ def nvfp4_block_scales(x: torch.Tensor) -> torch.Tensor:
     r, c = x.shape
     blk = x.to(torch.float32).reshape(r, c // NVFP4_BLOCK, NVFP4_BLOCK)
     amax = blk.abs().amax(dim=-1)
-    return (amax / E2M1_NORM_MAX).clamp(E4M3_SUBNORM_MIN, E4M3_NORM_MAX)
+    # a tensor divisor keeps this an IEEE division on every device (CUDA turns division by a
+    # Python scalar into a multiply by the reciprocal, which changes the last bit of some scales)
+    return (amax / torch.full_like(amax, E2M1_NORM_MAX)).clamp(E4M3_SUBNORM_MIN, E4M3_NORM_MAX)
 
 
 def nvfp4_quantize_rowwise(x: torch.Tensor, noise: torch.Tensor | None = None):

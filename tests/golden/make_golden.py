@@ -163,11 +163,15 @@ def main():
             qv, sw_ = fn(x)
             assert torch.equal(qv, q.contiguous())
             out[f"sw_{tag}"] = sw_.contiguous().numpy()
-            # stochastic rounding: the reference draws rand_like on the blocked (possibly transposed) tensor
+            # stochastic rounding: the reference draws rand_like on the blocked tensor.  Row-wise
+            # that tensor is contiguous [R, C/16, 16].  Column-wise it is a VIEW of the transposed
+            # input (strides (1, 16 C, C)), rand_like keeps those strides and fills memory order,
+            # so the stream is consumed in the layout of the original [R, C] tensor: the noise
+            # of element (r, c) is draw number r*C + c.
             torch.manual_seed(2000 + seed)
             qs, ss = fn(x, sr=True)
             torch.manual_seed(2000 + seed)
-            u = torch.rand(rows, cols // 16, 16) if rowwise else torch.rand(cols, rows // 16, 16)
+            u = torch.rand(rows, cols // 16, 16) if rowwise else torch.rand(rows, cols)
             out[f"sr_noise_{tag}"] = u.numpy()
             out[f"sr_q_{tag}"] = qs.numpy()
             assert torch.equal(ss, sw_)

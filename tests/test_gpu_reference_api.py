@@ -3,8 +3,9 @@
 calls (tests/golden/nvfp4_api_*.npz, swizzle_cases.npz; made by tests/golden/make_golden.py).
 
 Values, dtypes, shapes and scale bytes are compared exactly.  Stochastic rounding is compared
-with the reference's own noise: `torch.rand` is patched to hand back the stored draw, which
-has the blocked shape the reference consumes.  One documented difference: a value the
+with the reference's own noise: `torch.rand` is patched to hand back the stored draw (row-wise
+in the blocked shape [R, C/16, 16]; column-wise in the [R, C] layout in which the reference's
+strided `rand_like` consumes the stream).  One documented difference: a value the
 reference leaves at 8 (its pack kernel clips it to 6 later) comes back as 6 here; and a
 stochastic zero may carry either sign.
 """
