@@ -26,6 +26,7 @@ _SIGNATURES = {
     "fp4t_sf_bytes": (_c_i64, [_c_i64, _c_i64]),
     "fp4t_set_status_word": (ctypes.c_int, [_c_vp]),
     "fp4t_set_sm_limit": (ctypes.c_int, [ctypes.c_int]),
+    "fp4t_set_seed_offset_word": (ctypes.c_int, [_c_vp]),
     "fp4t_set_wait_timeout_ns": (ctypes.c_int, [ctypes.c_uint64]),
     "fp4t_reset_tile_counters": (ctypes.c_int, [ctypes.c_void_p]),
     "fp4t_allreduce_sum_bf16_multimem": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,

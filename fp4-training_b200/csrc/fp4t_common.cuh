@@ -68,6 +68,10 @@ int encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void
 // (set per host thread with fp4t_set_status_word, may be null).
 int32_t* current_status_word();
 
+// Device word added to the seed of in-kernel stochastic rounding when a kernel runs (null: none);
+// set per device with fp4t_set_seed_offset_word.
+const uint64_t* seed_offset_word();
+
 // Byte offset of scale (outer o, k-block i) in the 128x4 tile layout with `ntx`
 // tiles along the k-block axis.
 __host__ __device__ __forceinline__ int64_t sf_offset(int64_t o, int64_t i, int64_t ntx) {

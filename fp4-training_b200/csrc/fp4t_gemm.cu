@@ -352,7 +352,7 @@ __device__ __forceinline__ void emit_chunk(const GemmParams& g, const CUtensorMa
 template <int kFmt, int kBN, int kCtas>
 struct Cfg {
   static constexpr int kSfChunks = kFmt == kNvfp4 ? 4 : 1;   // 512-byte scale tiles per 128 rows per stage
-  static constexpr int kOuterB = kBN / 128;                  // 128-row scale tiles of Q per tile
+  static constexpr int kOuterB = (kBN + 127) / 128;          // 128-row scale tiles of Q per tile (a 64-column tile uses half of one)
   static constexpr int kABytes = kBM * 128;
   static constexpr int kBRows = kBN / kCtas;                 // Q rows this CTA loads
   static constexpr int kBBytes = kBRows * 128;
@@ -554,14 +554,14 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
           tma_load_2d_pair(sfa_s, &map_psf, bar, ks * C::kSfBoxElems, m_tile);
 #pragma unroll
           for (int o = 0; o < C::kOuterB; ++o)
-            tma_load_2d_pair(sfb_s + o * C::kSfaBytes, &map_qsf, bar, ks * C::kSfBoxElems, n_idx * C::kOuterB + o);
+            tma_load_2d_pair(sfb_s + o * C::kSfaBytes, &map_qsf, bar, ks * C::kSfBoxElems, (n_idx * kBN) / 128 + o);
           tma_load_2d_pair(a_s, &map_p, bar, ks * 128, row_p);
           tma_load_2d_pair(b_s, &map_q, bar, ks * 128, row_q);
         } else {
           tma_load_2d(sfa_s, &map_psf, bar, ks * C::kSfBoxElems, m_tile);
 #pragma unroll
           for (int o = 0; o < C::kOuterB; ++o)
-            tma_load_2d(sfb_s + o * C::kSfaBytes, &map_qsf, bar, ks * C::kSfBoxElems, n_idx * C::kOuterB + o);
+            tma_load_2d(sfb_s + o * C::kSfaBytes, &map_qsf, bar, ks * C::kSfBoxElems, (n_idx * kBN) / 128 + o);
           tma_load_2d(a_s, &map_p, bar, ks * 128, row_p);
           tma_load_2d(b_s, &map_q, bar, ks * 128, row_q);
         }
@@ -594,6 +594,9 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
         tc_fence_after();
       }
       const uint32_t acc = tmem_base + (uint32_t)((it & 1) * C::kAccStride);
+      // a 64-column tile starts in the middle of a 128-row scale tile of Q every other time:
+      // its 32-row groups are columns 2.. of the copied tile
+      const uint32_t sfb_shift = kBN < 128 ? (uint32_t)((((tile % g.n_tiles) * kBN) & 127) >> 5) : 0u;
       for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
         ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 23);
         if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
@@ -620,7 +623,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
             }
             const uint32_t id = kFmt == kNvfp4 ? idesc : (idesc | ((uint32_t)j << 29) | ((uint32_t)j << 4));
             tc_mma<kFmt, kCtas>(acc, make_desc(a_lo + 2 * j, kDescHiOperand), make_desc(b_lo + 2 * j, kDescHiOperand), id,
-                                j == 0 ? first : 1u, sfa_t, sfb_t);
+                                j == 0 ? first : 1u, sfa_t, sfb_t + sfb_shift);
           }
           tc_commit_all<kCtas>(bar_empty + 8 * stage);   // frees the stage in every CTA of the cluster
         }
@@ -831,6 +834,13 @@ int launch_best_width(const void* p_codes, const void* q_codes, const GemmParams
   const int64_t cm = ceil_div(g.m_tiles, kCtas);
   const double k256 = (double)ceil_div(cm * ceil_div(cols, 256), c256) * (128.0 + 256.0);
   const double k128 = (double)ceil_div(cm * ceil_div(cols, 128), c128) * (128.0 + 128.0);
+  if (kCtas == 1) {
+    // skinny outputs (at most 128 rows): the whole job is streaming Q once, so what matters is
+    // that every SM pulls; 64-column tiles double the number of CTAs at work
+    const int c64 = max_clusters<kFmt, 64, 1>();
+    const double k64 = c64 > 0 ? (double)ceil_div(cm * ceil_div(cols, 64), c64) * (128.0 + 64.0) : 1e30;
+    if (k64 < k128 && k64 < k256) return launch_gemm<kFmt, 64, 1>(p_codes, q_codes, g, kbytes, c64, stream);
+  }
   if (k256 <= k128) return launch_gemm<kFmt, 256, kCtas>(p_codes, q_codes, g, kbytes, c256, stream);
   return launch_gemm<kFmt, 128, kCtas>(p_codes, q_codes, g, kbytes, c128, stream);
 }

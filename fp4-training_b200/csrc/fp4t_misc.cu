@@ -29,6 +29,13 @@ int cuda_fail(cudaError_t e, const char* what) {
 static thread_local int32_t* g_status_word = nullptr;
 int32_t* current_status_word() { return g_status_word; }
 
+static std::atomic<const uint64_t*> g_seed_word[64];
+const uint64_t* seed_offset_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return g_seed_word[dev].load(std::memory_order_relaxed);
+}
+
 static std::atomic<int> g_sm_limit{0};
 int sm_limit() { return g_sm_limit.load(std::memory_order_relaxed); }
 
@@ -221,6 +228,15 @@ extern "C" int fp4t_set_wait_timeout_ns(uint64_t ns) {
 extern "C" int fp4t_set_sm_limit(int sms) {
   FP4T_REQUIRE(sms >= 0, "fp4t_set_sm_limit: negative limit");
   fp4t::g_sm_limit.store(sms, std::memory_order_relaxed);
+  return FP4T_OK;
+}
+
+extern "C" int fp4t_set_seed_offset_word(const uint64_t* device_word) {
+  int dev = 0;
+  FP4T_CUDA(cudaGetDevice(&dev));
+  FP4T_REQUIRE(dev >= 0 && dev < 64, "fp4t_set_seed_offset_word: device ordinal %d out of range", dev);
+  FP4T_REQUIRE(reinterpret_cast<uintptr_t>(device_word) % 8 == 0, "fp4t_set_seed_offset_word: the word must be 8-byte aligned");
+  fp4t::g_seed_word[dev].store(device_word, std::memory_order_relaxed);
   return FP4T_OK;
 }
 

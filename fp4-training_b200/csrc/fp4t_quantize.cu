@@ -33,6 +33,7 @@ struct QParams {
   const float* noise_t;
   float* colsum;   // optional fp32 [cols] accumulator of column sums (transposed pass only)
   uint64_t seed;
+  const uint64_t* seed_dev;   // optional device word added (times an odd constant) to `seed` when the kernel runs
   int ntx_row;  // scale tiles along k for the row-wise output
   int ntx_col;  // ... for the transposed output
 };
@@ -108,6 +109,7 @@ struct TileCtx {
   float* colsum_s;          // [4][128] partial column sums of this tile
   const float2* scale_tab;
   int64_t row0, col0;
+  uint64_t seed;            // effective seed of this launch
   int tid;
 };
 
@@ -129,7 +131,7 @@ __device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
   const int64_t out_step = kRowsPerIt * code_pitch;
   const uint8_t* src = c.tile + r_base * 256 + kb * (C::kBlk * 2);
   uint8_t* sf_dst = c.sf_row_s + (kb >> 2) * 512 + (kb & 3);
-  const uint32_t seed_lo = (uint32_t)p.seed, seed_hi = (uint32_t)(p.seed >> 32);
+  const uint32_t seed_lo = (uint32_t)c.seed, seed_hi = (uint32_t)(c.seed >> 32);
 
   // Phase 1: every load of the thread's kIts blocks is issued before any arithmetic, and every
   // store comes after all of it.  A store into the scale staging area may alias the tile as
@@ -239,7 +241,7 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
   if (kFmt == kNvfp4) {
     uint32_t outA[4], outB[4];
     uint32_t sfA[2], sfB[2];
-    const uint32_t seed_lo = (uint32_t)p.seed ^ 0x5BD1E995u, seed_hi = (uint32_t)(p.seed >> 32);
+    const uint32_t seed_lo = (uint32_t)c.seed ^ 0x5BD1E995u, seed_hi = (uint32_t)(c.seed >> 32);
     float sA[2], sB[2], rA[2], rB[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -390,6 +392,9 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
 
   const bool want_row = p.codes != nullptr;
   const bool want_col = p.codes_t != nullptr;
+  // A launch replayed from a CUDA graph carries the seed it was captured with; the optional
+  // device word (bumped by the host program between replays) makes every replay draw new noise.
+  const uint64_t seed = (kSr == FP4T_SR_HASH && p.seed_dev != nullptr) ? p.seed + __ldg(p.seed_dev) * 0x9E3779B97F4A7C15ull : p.seed;
 
   if (warp == kQComputeThreads / 32) {
     // ------------------------------ producer ------------------------------
@@ -451,6 +456,7 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
     c.sf_col_s = c.sf_row_s + C::kSfStage;
     c.colsum_s = colsum_stage + buf * 4 * kTile;
     c.scale_tab = scale_tab;
+    c.seed = seed;
     c.tid = tid;
     const bool interior = c.row0 + kTile <= p.rows && c.col0 + kTile <= p.cols;
     if (interior) {
@@ -514,6 +520,7 @@ __global__ void quantize_generic_kernel(const QParams p, const int transposed, c
   uint8_t* sf = transposed ? p.sf_t : p.sf;
   const float* noise = transposed ? p.noise_t : p.noise;
   const int64_t ntx = transposed ? p.ntx_col : p.ntx_row;
+  const uint64_t seed0 = (sr == FP4T_SR_HASH && p.seed_dev != nullptr) ? p.seed + __ldg(p.seed_dev) * 0x9E3779B97F4A7C15ull : p.seed;
   for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < total;
        b += (int64_t)gridDim.x * blockDim.x) {
     const int64_t o = b / kblocks, kb = b % kblocks;
@@ -534,7 +541,7 @@ __global__ void quantize_generic_kernel(const QParams p, const int transposed, c
         float y0 = __fdiv_rn(f[j], s), y1 = __fdiv_rn(f[j + 1], s);
         if (sr != FP4T_SR_NONE) {
           const int64_t e = o * inner + kb * kBlk + j;
-          const uint64_t seed = transposed ? (p.seed ^ 0x5bd1e995c2b2ae35ull) : p.seed;
+          const uint64_t seed = transposed ? (seed0 ^ 0x5bd1e995c2b2ae35ull) : seed0;
           const float u0 = sr == FP4T_SR_NOISE ? noise[e] : hash_uniform(seed, (uint64_t)e);
           const float u1 = sr == FP4T_SR_NOISE ? noise[e + 1] : hash_uniform(seed, (uint64_t)(e + 1));
           y0 = sr_round(y0, u0);
@@ -648,7 +655,7 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   p.x = x; p.rows = rows; p.cols = cols; p.ld = ld;
   p.codes = static_cast<uint8_t*>(codes); p.sf = static_cast<uint8_t*>(sf);
   p.codes_t = static_cast<uint8_t*>(codes_t); p.sf_t = static_cast<uint8_t*>(sf_t);
-  p.noise = noise; p.noise_t = noise_t; p.seed = seed; p.colsum = colsum;
+  p.noise = noise; p.noise_t = noise_t; p.seed = seed; p.seed_dev = seed_offset_word(); p.colsum = colsum;
   p.ntx_row = (int)ceil_div(ceil_div(cols, kBlk), 4);
   p.ntx_col = (int)ceil_div(ceil_div(rows, kBlk), 4);
 

@@ -6,7 +6,8 @@
  *   - enqueues its kernels on the given CUDA stream and returns without
  *     synchronising,
  *   - allocates nothing, creates no stream and keeps no reference to caller memory
- *     (one exception: fp4t_set_status_word stores the pointer it is given until it is replaced),
+ *     (exceptions: fp4t_set_status_word and fp4t_set_seed_offset_word store the pointer they are
+ *     given until it is replaced),
  *   - returns FP4T_OK (0) or a negative FP4T_ERR_* code; the text of the last
  *     error on the calling thread is available from fp4t_last_error().
  *
@@ -71,6 +72,19 @@ FP4T_API int fp4t_version(void);
  * memory and zeroes it.
  */
 FP4T_API int fp4t_set_status_word(int32_t* device_word);
+
+/*
+ * Stochastic rounding with FP4T_SR_HASH derives its noise from (seed, element index).  A launch
+ * that is replayed from a CUDA graph carries the seed it was captured with, so every replay
+ * would round with the same noise.  After this call, quantizer kernels launched on the CURRENT
+ * device add  *device_word * 0x9E3779B97F4A7C15  to their seed when they RUN: a program that
+ * increments the word between replays (on the stream, e.g. inside the graph) gets fresh noise
+ * each time.  The library keeps the pointer until it is replaced (null switches it off); the
+ * caller owns the memory.  Process-wide per device (the backward pass of an autograd engine
+ * runs on other host threads than the one that set it).  No counterpart in the reference,
+ * which draws torch.rand_like per call (custom/quantize.py:88).
+ */
+FP4T_API int fp4t_set_seed_offset_word(const uint64_t* device_word);
 
 /*
  * Every spin in the kernels (on an mbarrier, on a peer GPU's flag) is bounded: when the limit
