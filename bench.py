@@ -60,8 +60,8 @@ FP8_NOMINAL_TFLOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised
 # under profiles/ (fprop GEMM; quantizer of X).  Both working sets fit the 126 MB L2, so part
 # of the written data had not reached DRAM when the kernel ended.
-GEMM_DRAM_TRAFFIC = {"bytes": 47.3e6, "launch": "fprop 8192x4096x4096", "algorithmic_bytes": 94.4e6 / 3 + 67.1e6}
-QUANT_DRAM_TRAFFIC = {"bytes": 71.2e6, "launch": "X 8192x4096 row+transposed", "algorithmic_bytes": 3.125 * N * IC}
+GEMM_DRAM_TRAFFIC = {"bytes": 48.6e6, "launch": "fprop 8192x4096x4096", "algorithmic_bytes": 94.4e6 / 3 + 67.1e6}
+QUANT_DRAM_TRAFFIC = {"bytes": 71.6e6, "launch": "X 8192x4096 row+transposed", "algorithmic_bytes": 3.125 * N * IC}
 METRIC = "nvfp4_linear_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 WORKLOAD = "nvfp4_linear_fwd_bwd N=8192 IC=OC=4096 bf16 (quantize x3 + fprop/dgrad/wgrad)"
