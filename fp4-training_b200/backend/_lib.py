@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "..", "lib", "libfp4t.so")
 
 DT_BF16, DT_F32 = 0, 1
 SR_NONE, SR_NOISE, SR_HASH = 0, 1, 2
+QOUT_MXFP8, QOUT_NVFP4 = 1, 2
 
 _c_i64 = ctypes.c_int64
 _c_vp = ctypes.c_void_p
@@ -48,6 +49,10 @@ _SIGNATURES = {
                                         _c_i64, _c_vp, _c_vp]),
     "fp4t_gemm_mxfp8": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,
                                         _c_i64, _c_vp, _c_vp]),
+    "fp4t_gemm_nvfp4_qout": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64,
+                                             _c_i64, _c_i64, _c_vp, _c_vp]),
+    "fp4t_gemm_mxfp8_qout": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64,
+                                             _c_i64, _c_i64, _c_vp, _c_vp]),
     "fp4t_linear_workspace_bytes": (_c_i64, [ctypes.c_int, _c_i64, _c_i64, _c_i64]),
     "fp4t_linear_backward_workspace_bytes": (_c_i64, [ctypes.c_int, _c_i64, _c_i64]),
     "fp4t_linear_forward": (ctypes.c_int, [ctypes.c_int, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, ctypes.c_int,

@@ -198,6 +198,36 @@ def gemm_mxfp8(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16
     return _gemm("mxfp8", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out)
 
 
+def gemm_qout(fmt, p_codes, p_sf, q_codes, q_sf, bias=None, out_fmt="mxfp8"):
+    """D = P . Q^T (+bias) written as a block-quantized row-wise operand: -> (codes, sf) with
+    codes [rows, cols] E4M3 bytes (out_fmt 'mxfp8') or [rows, cols/2] packed E2M1 ('nvfp4') and the
+    scales of logical [rows, cols/32] or [rows, cols/16] in the tile layout."""
+    _need_cuda(p_codes, p_sf, q_codes, q_sf, bias)
+    rows, cols = p_codes.shape[0], q_codes.shape[0]
+    kbytes = p_codes.shape[1]
+    if q_codes.shape[1] != kbytes:
+        raise RuntimeError(f"Mismatch matmul inner: P has {kbytes} code bytes per row, Q has {q_codes.shape[1]}")
+    if cols % 32:
+        raise ValueError("a quantized GEMM output needs a multiple of 32 columns")
+    k = kbytes * 2 if fmt == "nvfp4" else kbytes
+    dev = p_codes.device
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    blk = 16 if out_fmt == "nvfp4" else 32
+    with _on_device(dev):
+        codes = torch.empty((rows, cols // 2 if out_fmt == "nvfp4" else cols), dtype=torch.uint8, device=dev)
+        sf = torch.empty(_lib.sf_shape(rows, cols // blk), dtype=torch.uint8, device=dev)
+        if rows == 0 or cols == 0:
+            return codes, sf
+        fn = _lib.lib().fp4t_gemm_nvfp4_qout if fmt == "nvfp4" else _lib.lib().fp4t_gemm_mxfp8_qout
+        rc = fn(_lib.ptr(p_codes), _lib.ptr(p_sf), _lib.ptr(q_codes), _lib.ptr(q_sf), _lib.ptr(bias), _lib.ptr(codes),
+                _lib.ptr(sf), _lib.QOUT_NVFP4 if out_fmt == "nvfp4" else _lib.QOUT_MXFP8, codes.stride(0), rows, cols, k,
+                _lib.ptr(status_word(dev)), _lib.stream_ptr(dev))
+        _lib.check(rc, f"fp4t_gemm_{fmt}_qout")
+        LAUNCHES["gemm"] += 1
+    return codes, sf
+
+
 def pack_e2m1(values: torch.Tensor) -> torch.Tensor:
     """fp32/bf16 values on the E2M1 grid [R, C] -> packed codes [R, C/2]."""
     _need_cuda(values)

@@ -44,9 +44,22 @@ def _check_common(A, scaleA, B, scaleB):
 
 
 def _check_dout(dt):
-    if dt not in (torch.float32, torch.bfloat16):
-        raise RuntimeError("Only torch.float32 and torch.bfloat16 are supported for Dout by this build; "
-                           f"but found {dt}")
+    if dt not in (torch.float32, torch.bfloat16, torch.uint8):
+        raise RuntimeError("Only torch.float32, torch.bfloat16 and torch.uint8 (block-quantized output) are "
+                           f"supported for Dout; but found {dt}")
+
+
+def _qout(fmt, out_fmt, p, p_sf, q, q_sf, bias, m, n):
+    """Dout = uint8: the output leaves as block-quantized codes with its own scales
+    (custom/backend/csrc/cublaslt_mm_mxfp8.cu:155-161,247-253; the NVFP4 counterpart is a TODO at
+    cublaslt_mm_nvfp4.cu:241-247).  scaleDout holds the tile-layout bytes; it is returned with the
+    2-D shape the reference allocates, [roundoff(m / block, 4), roundoff(n, 128)]."""
+    blk = 32 if out_fmt == "mxfp8" else 16
+    if m % 32:
+        raise RuntimeError("When Dout is FP8/FP4 (stored as uint8), batch size m must be a multiple of 32; "
+                           f"got m={m}.")
+    codes, sf = ops.gemm_qout(fmt, p, p_sf, q, q_sf, bias, out_fmt)
+    return codes, sf.reshape((m // blk + 3) // 4 * 4, (n + 127) // 128 * 128)
 
 
 def _addmm_cuda(a, b, c=None):
@@ -94,6 +107,8 @@ def _mm_nvfp4(mode, DoutType, A, scaleA, B, scaleB, bias=None):
     if bias is not None and (bias.ndim != 1 or bias.shape[0] != A.shape[0]):
         raise RuntimeError(f"bias is expected to be 1D of length {A.shape[0]}, but got shape {tuple(bias.shape)}")
     qa, qb = ops.pack_e2m1(A), ops.pack_e2m1(B)
+    if DoutType == torch.uint8:
+        return _qout("nvfp4", "nvfp4", qb, scaleB, qa, scaleA, bias, A.shape[0], B.shape[0])
     out = ops.gemm_nvfp4(qb, scaleB, qa, scaleA, bias, DoutType)
     return out, out.new_empty(0)
 
@@ -123,6 +138,8 @@ def _mm_mxfp8(mode, DoutType, A, scaleA, B, scaleB, bias=None):
         raise RuntimeError(f"Mismatch matmul inner: A's k = {q.shape[1]}, B's k = {p.shape[1]}")
     if bias is not None and (bias.ndim != 1 or bias.shape[0] != q.shape[0]):
         raise RuntimeError(f"bias is expected to be 1D of length {q.shape[0]}, but got shape {tuple(bias.shape)}")
+    if DoutType == torch.uint8:
+        return _qout("mxfp8", "mxfp8", p, p_sf, q, q_sf, bias, q.shape[0], p.shape[0])
     out = ops.gemm_mxfp8(p, p_sf, q, q_sf, bias, DoutType)
     return out, out.new_empty(0)
 

@@ -76,6 +76,9 @@ struct GemmParams {
   int vec_ok;       // 16-byte stores allowed
   int tma_ok;       // the output can be written with tiled TMA stores
   int sched;        // tile-counter slot of the launching stream, or -1 for the static order
+  int out_q;        // 0: bf16 / fp32 output; FP4T_QOUT_MXFP8 / FP4T_QOUT_NVFP4: block-quantized output
+  uint8_t* d_sf;    // scale bytes of the quantized output (128x4 tile layout of logical [rows, cols / block])
+  int d_ntx;        // scale tiles along the columns of the quantized output
   int32_t* status;
 };
 
@@ -344,6 +347,60 @@ __device__ __forceinline__ void emit_chunk(const GemmParams& g, const CUtensorMa
     }
   }
   ++n_emit;
+}
+
+// Epilogue of one 32-column chunk as a block-quantized operand: the lane's 32 accumulators
+// (+ bias) become one MXFP8 block (E4M3 codes, UE8M0 scale) or two NVFP4 blocks (E2M1 codes,
+// UE4M3 scales), written row-major with the scales in the tile layout -- the row-wise operand
+// form the next GEMM reads.  Same arithmetic as the quantizers' general (fp32-input) path:
+// true divisions, E4M3 elements rounded half away from zero, E2M1 round-to-nearest-even.
+__device__ __forceinline__ void quant_chunk(const GemmParams& g, const int row, const bool row_ok, const int col0,
+                                            const uint32_t (&r)[32]) {
+  if (!row_ok || col0 >= g.cols) return;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (g.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(g.bias[col0 + j]);
+  }
+  if (g.out_q == FP4T_QOUT_MXFP8) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    const uint32_t sb = mx_scale_byte(amax);
+    const float inv = mx_inv_scale(sb);
+    uint32_t w[8];
+#pragma unroll
+    for (int q4 = 0; q4 < 8; ++q4) {
+      w[q4] = mx_e4m3_byte<true>(v[4 * q4] * inv) | (mx_e4m3_byte<true>(v[4 * q4 + 1] * inv) << 8) |
+              (mx_e4m3_byte<true>(v[4 * q4 + 2] * inv) << 16) | (mx_e4m3_byte<true>(v[4 * q4 + 3] * inv) << 24);
+    }
+    uint8_t* dp = static_cast<uint8_t*>(g.d) + (int64_t)row * g.ldd + col0;
+    reinterpret_cast<uint4*>(dp)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(dp)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    g.d_sf[sf_offset(row, col0 >> 5, g.d_ntx)] = (uint8_t)sb;
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      float amax = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[16 * b + j]));
+      const float s = nvfp4_scale(amax);
+      float y[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float t = __fdiv_rn(v[16 * b + j], s);
+        y[j] = t == 0.0f ? 0.0f : t;     // sign(+-0) is 0
+      }
+      w[2 * b] = cvt_e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
+      w[2 * b + 1] = cvt_e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
+      g.d_sf[sf_offset(row, (col0 >> 4) + b, g.d_ntx)] = (uint8_t)cvt_e4m3(s);
+    }
+    uint8_t* dp = static_cast<uint8_t*>(g.d) + (int64_t)row * g.ldd + (col0 >> 1);
+    *reinterpret_cast<uint4*>(dp) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -660,7 +717,8 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       const bool row_ok = row < g.rows;
       const int col_base = n_idx * kBN;
       auto put = [&](int col0, const uint32_t (&r)[32]) {
-        if (g.tma_ok) emit_chunk(g, &map_d, epi_buf, n_emit, lane, row0, col0, r);
+        if (g.out_q) quant_chunk(g, row, row_ok, col0, r);
+        else if (g.tma_ok) emit_chunk(g, &map_d, epi_buf, n_emit, lane, row0, col0, r);
         else store_chunk(g, row, row_ok, col0, r);
       };
       auto release = [&]() {     // the other accumulator's columns are free: the MMA warp may start the next tile
@@ -848,15 +906,25 @@ int launch_best_width(const void* p_codes, const void* q_codes, const GemmParams
 template <int kFmt>
 int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf, const void* bias,
                   void* d, int d_dtype, int64_t ldd, int64_t rows, int64_t cols, int64_t k, int32_t* status,
-                  cudaStream_t stream) {
-  const char* name = kFmt == kNvfp4 ? "fp4t_gemm_nvfp4" : "fp4t_gemm_mxfp8";
+                  cudaStream_t stream, int out_q = 0, void* d_sf = nullptr) {
+  const char* name = out_q ? (kFmt == kNvfp4 ? "fp4t_gemm_nvfp4_qout" : "fp4t_gemm_mxfp8_qout")
+                           : (kFmt == kNvfp4 ? "fp4t_gemm_nvfp4" : "fp4t_gemm_mxfp8");
   constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
   FP4T_REQUIRE(p_codes && p_sf && q_codes && q_sf && d, "%s: null pointer", name);
+  if (out_q) {
+    FP4T_REQUIRE(out_q == FP4T_QOUT_MXFP8 || out_q == FP4T_QOUT_NVFP4, "%s: out_fmt must be FP4T_QOUT_MXFP8 or FP4T_QOUT_NVFP4", name);
+    FP4T_REQUIRE(d_sf != nullptr, "%s: d_sf is null", name);
+    FP4T_REQUIRE(cols % 32 == 0, "%s: a quantized output needs cols %% 32 == 0 (cols=%lld)", name, (long long)cols);
+    FP4T_REQUIRE(reinterpret_cast<uintptr_t>(d) % 16 == 0 && ldd % 16 == 0,
+                 "%s: quantized output rows must be 16-byte aligned (ldd is in bytes of codes)", name);
+    d_dtype = FP4T_DT_BF16;   // unused by the quantizing epilogue
+  }
   FP4T_REQUIRE(d_dtype == FP4T_DT_BF16 || d_dtype == FP4T_DT_F32, "%s: output dtype must be bf16 or f32", name);
   FP4T_REQUIRE(rows >= 0 && cols >= 0 && k > 0, "%s: bad shape rows=%lld cols=%lld k=%lld", name, (long long)rows,
                (long long)cols, (long long)k);
   FP4T_REQUIRE(rows < (1ll << 31) && cols < (1ll << 31) && k < (1ll << 31), "%s: dimension exceeds 2^31", name);
-  FP4T_REQUIRE(ldd >= cols, "%s: ldd (%lld) < cols (%lld)", name, (long long)ldd, (long long)cols);
+  FP4T_REQUIRE(ldd >= (out_q == FP4T_QOUT_NVFP4 ? cols / 2 : cols), "%s: ldd (%lld) too small for cols (%lld)", name,
+               (long long)ldd, (long long)cols);
   if (kFmt == kNvfp4) FP4T_REQUIRE(k % 32 == 0, "%s: K must be a multiple of 32 (K=%lld)", name, (long long)k);
   else FP4T_REQUIRE(k % 16 == 0, "%s: K must be a multiple of 16 (K=%lld)", name, (long long)k);
   FP4T_REQUIRE(reinterpret_cast<uintptr_t>(p_codes) % 16 == 0 && reinterpret_cast<uintptr_t>(q_codes) % 16 == 0 &&
@@ -890,6 +958,14 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
   g.sched = sched_slot_for(stream);
   g.status = status;
   g.n_tiles = 0;
+  g.out_q = out_q;
+  g.d_sf = static_cast<uint8_t*>(d_sf);
+  g.d_ntx = out_q ? (int)ceil_div(cols / (out_q == FP4T_QOUT_NVFP4 ? 16 : 32), 4) : 0;
+  if (out_q) {
+    g.tma_ok = 0;   // the quantizing epilogue stores from registers
+    // rows and column blocks that pad the scale buffer to whole tiles must read as zero
+    FP4T_CUDA(cudaMemsetAsync(d_sf, 0, (size_t)fp4t_sf_bytes(rows, cols / (out_q == FP4T_QOUT_NVFP4 ? 16 : 32)), stream));
+  }
 
   // CTA pairs whenever there are at least two 128-row tiles (FP4T_GEMM_1CTA=1 keeps the
   // single-CTA form, for comparisons).
@@ -922,4 +998,18 @@ extern "C" int fp4t_gemm_mxfp8(const void* p_codes, const void* p_sf, const void
                                int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream) {
   return fp4t::gemm_dispatch<fp4t::kMxfp8>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d, d_dtype, ldd, rows, cols, k,
                                            status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fp4t_gemm_nvfp4_qout(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                                    const void* bias_bf16, void* d_codes, void* d_sf, int out_fmt, int64_t ldd,
+                                    int64_t rows, int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream) {
+  return fp4t::gemm_dispatch<fp4t::kNvfp4>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d_codes, FP4T_DT_BF16, ldd, rows, cols,
+                                           k, status, reinterpret_cast<cudaStream_t>(stream), out_fmt, d_sf);
+}
+
+extern "C" int fp4t_gemm_mxfp8_qout(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                                    const void* bias_bf16, void* d_codes, void* d_sf, int out_fmt, int64_t ldd,
+                                    int64_t rows, int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream) {
+  return fp4t::gemm_dispatch<fp4t::kMxfp8>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d_codes, FP4T_DT_BF16, ldd, rows, cols,
+                                           k, status, reinterpret_cast<cudaStream_t>(stream), out_fmt, d_sf);
 }

@@ -228,6 +228,29 @@ FP4T_API int fp4t_gemm_mxfp8(const void* p_codes, const void* p_sf, const void* 
                     fp4t_stream_t stream);
 
 /*
+ * The same GEMMs with a block-quantized OUTPUT: the epilogue turns each row's 32-column pieces
+ * of the fp32 accumulator (+ bias) into the row-wise operand of a following GEMM whose K is
+ * this GEMM's `cols`, so a chain GEMM -> GEMM needs no bf16 round trip and no quantizer launch:
+ *   out_fmt FP4T_QOUT_MXFP8  d_codes [rows, cols] E4M3 bytes, d_sf ~ logical [rows, cols/32] UE8M0
+ *   out_fmt FP4T_QOUT_NVFP4  d_codes [rows, cols/2] packed E2M1, d_sf ~ logical [rows, cols/16] UE4M3
+ * (scales in the tile layout; the call zeroes the scale buffer's padding on the stream).  ldd is
+ * the pitch of d_codes in BYTES (a multiple of 16); cols must be a multiple of 32.  The
+ * conversion is the quantizers' (true divisions; E4M3 elements round half away from zero, E2M1
+ * to nearest even), applied to the fp32 accumulator instead of a bf16 tensor.
+ *
+ * Finishes what custom/backend/csrc/cublaslt_mm_mxfp8.cu:155-161,247-253 (Dout = uint8: E4M3
+ * output + scaleDout) and cublaslt_mm_nvfp4.cu:241-247,374-380 (Dout = uint8: E2M1 output,
+ * marked TODO there) start through cuBLASLt's D_OUT scale mode.
+ */
+enum { FP4T_QOUT_MXFP8 = 1, FP4T_QOUT_NVFP4 = 2 };
+FP4T_API int fp4t_gemm_nvfp4_qout(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                         const void* bias_bf16, void* d_codes, void* d_sf, int out_fmt, int64_t ldd,
+                         int64_t rows, int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream);
+FP4T_API int fp4t_gemm_mxfp8_qout(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                         const void* bias_bf16, void* d_codes, void* d_sf, int out_fmt, int64_t ldd,
+                         int64_t rows, int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream);
+
+/*
  * A whole linear layer per call.  fmt: 0 = NVFP4, 1 = MXFP8.
  *
  * fp4t_linear_forward quantizes W [oc, ic] and X [n, ic] (emitting the transposed operands of
