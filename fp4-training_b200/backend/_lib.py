@@ -54,7 +54,12 @@ _SIGNATURES = {
     "fp4t_gemm_mxfp8_qout": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64,
                                              _c_i64, _c_i64, _c_vp, _c_vp]),
     "fp4t_linear_workspace_bytes": (_c_i64, [ctypes.c_int, _c_i64, _c_i64, _c_i64]),
-    "fp4t_linear_backward_workspace_bytes": (_c_i64, [ctypes.c_int, _c_i64, _c_i64]),
+    "fp4t_linear_backward_workspace_bytes": (_c_i64, [ctypes.c_int, _c_i64, _c_i64, _c_i64]),
+    "fp4t_gemm_splitk_workspace_bytes": (_c_i64, [_c_i64, _c_i64]),
+    "fp4t_gemm_nvfp4_splitk": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,
+                                               _c_i64, _c_vp, _c_i64, _c_vp, _c_vp]),
+    "fp4t_gemm_mxfp8_splitk": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,
+                                               _c_i64, _c_vp, _c_i64, _c_vp, _c_vp]),
     "fp4t_linear_forward": (ctypes.c_int, [ctypes.c_int, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, ctypes.c_int,
                                             _c_i64, _c_i64, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_vp, ctypes.c_int, _c_vp,
                                             _c_vp]),

@@ -162,7 +162,7 @@ def quantize_mxfp8(x, want_row=True, want_t=False, bias_grad_dtype=None):
     return _quantize("mxfp8", x, want_row, want_t, SR_NONE, None, None, 0, bias_grad_dtype)
 
 
-def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None):
+def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None, split_k=True):
     _need_cuda(p_codes, p_sf, q_codes, q_sf, bias)
     rows, cols = p_codes.shape[0], q_codes.shape[0]
     kbytes = p_codes.shape[1]
@@ -179,23 +179,33 @@ def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None):
             out = torch.empty((rows, cols), dtype=out_dtype, device=dev)
         if rows == 0 or cols == 0:
             return out
-        fn = _lib.lib().fp4t_gemm_nvfp4 if fmt == "nvfp4" else _lib.lib().fp4t_gemm_mxfp8
-        rc = fn(_lib.ptr(p_codes), _lib.ptr(p_sf), _lib.ptr(q_codes), _lib.ptr(q_sf), _lib.ptr(bias),
-                _lib.ptr(out), _lib.dtype_code(out.dtype), out.stride(0), rows, cols, k,
-                _lib.ptr(status_word(dev)), _lib.stream_ptr(dev))
+        L = _lib.lib()
+        ws_bytes = L.fp4t_gemm_splitk_workspace_bytes(rows, cols) if (split_k and k >= 2048) else 0
+        if ws_bytes > 0:      # a small output over a long K: let the idle SMs share the K loop
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            fn = L.fp4t_gemm_nvfp4_splitk if fmt == "nvfp4" else L.fp4t_gemm_mxfp8_splitk
+            rc = fn(_lib.ptr(p_codes), _lib.ptr(p_sf), _lib.ptr(q_codes), _lib.ptr(q_sf), _lib.ptr(bias),
+                    _lib.ptr(out), _lib.dtype_code(out.dtype), out.stride(0), rows, cols, k, _lib.ptr(ws), ws_bytes,
+                    _lib.ptr(status_word(dev)), _lib.stream_ptr(dev))
+        else:
+            fn = L.fp4t_gemm_nvfp4 if fmt == "nvfp4" else L.fp4t_gemm_mxfp8
+            rc = fn(_lib.ptr(p_codes), _lib.ptr(p_sf), _lib.ptr(q_codes), _lib.ptr(q_sf), _lib.ptr(bias),
+                    _lib.ptr(out), _lib.dtype_code(out.dtype), out.stride(0), rows, cols, k,
+                    _lib.ptr(status_word(dev)), _lib.stream_ptr(dev))
         _lib.check(rc, f"fp4t_gemm_{fmt}")
         LAUNCHES["gemm"] += 1
     return out
 
 
-def gemm_nvfp4(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None):
-    """D[rows, cols] = P . Q^T (+bias); P/Q packed E2M1 codes [outer, K/2]."""
-    return _gemm("nvfp4", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out)
+def gemm_nvfp4(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None, split_k=True):
+    """D[rows, cols] = P . Q^T (+bias); P/Q packed E2M1 codes [outer, K/2].  split_k=False keeps
+    a small-output / long-K product on the unsplit kernel (one fixed accumulation order)."""
+    return _gemm("nvfp4", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out, split_k)
 
 
-def gemm_mxfp8(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None):
+def gemm_mxfp8(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None, split_k=True):
     """D[rows, cols] = P . Q^T (+bias); P/Q E4M3 codes [outer, K]."""
-    return _gemm("mxfp8", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out)
+    return _gemm("mxfp8", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out, split_k)
 
 
 def gemm_qout(fmt, p_codes, p_sf, q_codes, q_sf, bias=None, out_fmt="mxfp8"):
@@ -340,7 +350,7 @@ def linear_backward(fmt, g, ws, ic, need_dx, need_dw, need_db, sr=SR_NONE, noise
     with _on_device(dev):
         L = _lib.lib()
         _bind_status(dev)
-        bws = torch.empty(L.fp4t_linear_backward_workspace_bytes(_FMT[fmt], n, oc), dtype=torch.uint8, device=dev)
+        bws = torch.empty(L.fp4t_linear_backward_workspace_bytes(_FMT[fmt], n, oc, ic), dtype=torch.uint8, device=dev)
         dx = torch.empty((n, ic), dtype=g.dtype, device=dev) if need_dx else None
         dw = (out_dw if out_dw is not None else torch.empty((oc, ic), dtype=g.dtype, device=dev)) if need_dw else None
         db = (out_db if out_db is not None else torch.empty((oc,), dtype=g.dtype, device=dev)) if need_db else None

@@ -76,6 +76,9 @@ struct GemmParams {
   int vec_ok;       // 16-byte stores allowed
   int tma_ok;       // the output can be written with tiled TMA stores
   int sched;        // tile-counter slot of the launching stream, or -1 for the static order
+  int splits;       // > 1: split-K, split s of a tile accumulates K stages [s ks_per_split, ...) into slice s of a fp32 workspace
+  int ks_per_split;
+  int slice_rows;   // rows of one workspace slice (a multiple of the cluster tile height)
   int out_q;        // 0: bf16 / fp32 output; FP4T_QOUT_MXFP8 / FP4T_QOUT_NVFP4: block-quantized output
   uint8_t* d_sf;    // scale bytes of the quantized output (128x4 tile layout of logical [rows, cols / block])
   int d_ntx;        // scale tiles along the columns of the quantized output
@@ -286,7 +289,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& g, const int row, 
 // `buf` is this warp's staging area (4 KB, 1024-byte aligned): two 2-KB tiles for bf16 output
 // that alternate, one 4-KB tile for fp32 output.
 __device__ __forceinline__ void emit_chunk(const GemmParams& g, const CUtensorMap* map_d, uint8_t* buf, uint32_t& n_emit,
-                                           const int lane, const int row0, const int col0, const uint32_t (&r)[32]) {
+                                           const int lane, const int row0, const int row_store, const int col0,
+                                           const uint32_t (&r)[32]) {
+  // row0: first row of the chunk in the logical output (bounds); row_store: its row in the
+  // tensor map (the same, or shifted into the split's workspace slice)
   if (row0 >= g.rows || col0 >= g.cols) return;   // warp-uniform
   float v[32];
 #pragma unroll
@@ -321,7 +327,7 @@ __device__ __forceinline__ void emit_chunk(const GemmParams& g, const CUtensorMa
     fence_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(map_d, smem_u32(buf), col0, row0);
+      tma_store_2d(map_d, smem_u32(buf), col0, row_store);
       bulk_commit();
     }
   } else {
@@ -342,7 +348,7 @@ __device__ __forceinline__ void emit_chunk(const GemmParams& g, const CUtensorMa
     fence_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(map_d, smem_u32(tile), col0, row0);
+      tma_store_2d(map_d, smem_u32(tile), col0, row_store);
       bulk_commit();
     }
   }
@@ -521,7 +527,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
 
   // cluster tile = (128 * kCtas) rows x kBN columns
   const int pair_m_tiles = (g.m_tiles + kCtas - 1) / kCtas;
-  const int num_tiles = pair_m_tiles * g.n_tiles;
+  const int num_tiles = pair_m_tiles * g.n_tiles * g.splits;   // work units: (tile, K split)
   const uint32_t leader_full = kPair ? mapa_u32(bar_full, 0) : bar_full;
   const uint32_t leader_tmem_empty = kPair ? mapa_u32(bar_tmem_empty, 0) : bar_tmem_empty;
   const uint32_t leader_sched_empty = kPair ? mapa_u32(bar_sched_empty, 0) : bar_sched_empty;
@@ -591,13 +597,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
     uint32_t phase = 0;
     bool ok = true;
     for (uint32_t tn = 0; ok; ++tn) {
-      const int tile = sched_next(tn, 31);
-      if (tile < 0) break;
+      const int unit = sched_next(tn, 31);
+      if (unit < 0) break;
+      const int tile = unit / g.splits, split = unit - tile * g.splits;
+      const int ks0 = split * g.ks_per_split, ks1 = min(ks0 + g.ks_per_split, g.k_stages);
       const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
       const int m_tile = pm * kCtas + (int)rank;              // this CTA's 128-row tile of P
       const int row_p = m_tile * kBM;
       const int row_q = n_idx * kBN + (int)rank * C::kBRows;  // this CTA's share of the Q rows
-      for (int ks = 0; ks < g.k_stages; ++ks) {
+      for (int ks = ks0; ks < ks1; ++ks) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, g.status, 21)) { ok = false; break; }
         const uint32_t a_s = smem_base + stage * C::kStageBytes;
         const uint32_t b_s = a_s + C::kABytes;
@@ -641,10 +649,12 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
     uint32_t k = 0;          // stages issued so far
     bool ok = true;
     for (int it = 0; ok; ++it) {
-      int tile = 0;
-      if (lane == 0) tile = sched_next((uint32_t)it, 33);
-      tile = __shfl_sync(0xFFFFFFFFu, tile, 0);
-      if (tile < 0) break;
+      int unit = 0;
+      if (lane == 0) unit = sched_next((uint32_t)it, 33);
+      unit = __shfl_sync(0xFFFFFFFFu, unit, 0);
+      if (unit < 0) break;
+      const int tile = unit / g.splits, split = unit - tile * g.splits;
+      const int ks0 = split * g.ks_per_split, ks1 = min(ks0 + g.ks_per_split, g.k_stages);
       if (it > 0) {
         ok = mbar_wait(bar_tmem_empty, (uint32_t)((it - 1) & 1), abort_flag, g.status, 22);
         if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
@@ -654,7 +664,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       // a 64-column tile starts in the middle of a 128-row scale tile of Q every other time:
       // its 32-row groups are columns 2.. of the copied tile
       const uint32_t sfb_shift = kBN < 128 ? (uint32_t)((((tile % g.n_tiles) * kBN) & 127) >> 5) : 0u;
-      for (int ks = 0; ks < g.k_stages; ++ks, ++k) {
+      for (int ks = ks0; ks < ks1; ++ks, ++k) {
         ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, 23);
         if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
         tc_fence_after();
@@ -663,7 +673,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
           const uint32_t b_lo = a_lo + (C::kABytes >> 4);
           const uint32_t sfa_lo = a_lo + (C::kSfaOff >> 4);
           const uint32_t sfb_lo = a_lo + (C::kSfbOff >> 4);
-          const uint32_t first = ks > 0 ? 1u : 0u;
+          const uint32_t first = ks > ks0 ? 1u : 0u;
           // Scale tile c of P's rows and tiles (o, c) of Q's rows go to the set the MMA reads.  K
           // beyond the matrix is zero codes times zero scales, so every stage issues all four MMAs.
 #pragma unroll
@@ -701,10 +711,11 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
     uint32_t n_emit = 0;
     int it = 0;
     for (;; ++it) {
-      int tile = 0;
-      if (lane == 0) tile = sched_next((uint32_t)it, 35);
-      tile = __shfl_sync(0xFFFFFFFFu, tile, 0);
-      if (tile < 0) break;
+      int unit = 0;
+      if (lane == 0) unit = sched_next((uint32_t)it, 35);
+      unit = __shfl_sync(0xFFFFFFFFu, unit, 0);
+      if (unit < 0) break;
+      const int tile = unit / g.splits, split = unit - tile * g.splits;
       const int pm = tile / g.n_tiles, n_idx = tile % g.n_tiles;
       int ok = 1;
       if (lane == 0) ok = mbar_wait(bar_tmem_full, (uint32_t)(it & 1), abort_flag, g.status, 24) ? 1 : 0;
@@ -718,7 +729,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       const int col_base = n_idx * kBN;
       auto put = [&](int col0, const uint32_t (&r)[32]) {
         if (g.out_q) quant_chunk(g, row, row_ok, col0, r);
-        else if (g.tma_ok) emit_chunk(g, &map_d, epi_buf, n_emit, lane, row0, col0, r);
+        else if (g.tma_ok) emit_chunk(g, &map_d, epi_buf, n_emit, lane, row0, row0 + split * g.slice_rows, col0, r);
         else store_chunk(g, row, row_ok, col0, r);
       };
       auto release = [&]() {     // the other accumulator's columns are free: the MMA warp may start the next tile
@@ -776,6 +787,23 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
     else
       asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
                    : "memory");
+  }
+}
+
+// Split-K finish: out[r, c] = sum over the splits' fp32 slices (+ bias[c]), in the output dtype.
+__global__ void splitk_finalize_kernel(const float* __restrict__ ws, int splits, int64_t slice_elems, void* __restrict__ d,
+                                       int out_f32, int64_t ldd, int rows, int cols,
+                                       const __nv_bfloat16* __restrict__ bias) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = (int64_t)rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols), c = (int)(i - (int64_t)r * cols);
+    float acc = 0.0f;
+    for (int s = 0; s < splits; ++s) acc += ws[s * slice_elems + i];
+    if (bias != nullptr) acc += __bfloat162float(bias[c]);
+    if (out_f32) static_cast<float*>(d)[(int64_t)r * ldd + c] = acc;
+    else static_cast<__nv_bfloat16*>(d)[(int64_t)r * ldd + c] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -852,12 +880,13 @@ int launch_gemm(const void* p_codes, const void* q_codes, const GemmParams& g0, 
   if (rc != FP4T_OK) return rc;
   CUtensorMap map_d = {};
   if (g.tma_ok) {   // 32 x 32 element boxes; the swizzle width equals the box row (64 B bf16, 128 B fp32)
+    const uint64_t d_rows = g.splits > 1 ? (uint64_t)g.splits * g.slice_rows : (uint64_t)g.rows;
     rc = encode_tensor_map_2d(&map_d, g.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                              g.d, (uint64_t)g.cols, (uint64_t)g.rows, (uint64_t)g.ldd * (g.out_f32 ? 4 : 2), 32u, 32u,
+                              g.d, (uint64_t)g.cols, d_rows, (uint64_t)g.ldd * (g.out_f32 ? 4 : 2), 32u, 32u,
                               g.out_f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc != FP4T_OK) return rc;
   }
-  const int cluster_tiles = (int)ceil_div(g.m_tiles, kCtas) * g.n_tiles;
+  const int cluster_tiles = (int)ceil_div(g.m_tiles, kCtas) * g.n_tiles * g.splits;
   const int lim = sm_limit();
   if (lim > 0 && lim / kCtas < clusters) clusters = lim / kCtas > 0 ? lim / kCtas : 1;
   const int nclusters = cluster_tiles < clusters ? cluster_tiles : clusters;
@@ -879,9 +908,60 @@ int launch_gemm(const void* p_codes, const void* q_codes, const GemmParams& g0, 
   return FP4T_OK;
 }
 
+// Optional split-K resources of a call: a caller-owned fp32 workspace.
+struct SplitK {
+  void* ws = nullptr;
+  int64_t ws_bytes = 0;
+};
+
+// Launches the kernel of width kBN; with a workspace, and when the output has so few tiles that
+// most SMs would idle (the wgrad of a small layer over a long batch: 192 x 192 x 25600 is ONE
+// tile), the K loop is split over the idle clusters: split s of a tile writes its fp32 partial
+// to slice s of the workspace and a small kernel adds the slices (+ bias) into the output.
+template <int kFmt, int kBN, int kCtas>
+int launch_maybe_split(const void* p_codes, const void* q_codes, const GemmParams& g, int64_t kbytes, int clusters,
+                       const SplitK& sk, cudaStream_t stream) {
+  const int64_t cm = ceil_div(g.m_tiles, kCtas);
+  const int64_t tiles = cm * ceil_div(g.cols, kBN);
+  int splits = 1;
+  const int64_t slice_rows = cm * kCtas * kBM;
+  if (sk.ws != nullptr && !g.out_q && tiles * 2 <= clusters && g.k_stages >= 4) {
+    int64_t s = clusters / tiles;
+    if (s > g.k_stages / 2) s = g.k_stages / 2;
+    const int64_t slice_bytes = slice_rows * g.cols * 4;
+    if (s * slice_bytes > sk.ws_bytes) s = sk.ws_bytes / slice_bytes;
+    if (s >= 2) splits = (int)s;
+  }
+  if (splits == 1) return launch_gemm<kFmt, kBN, kCtas>(p_codes, q_codes, g, kbytes, clusters, stream);
+  GemmParams gs = g;
+  gs.ks_per_split = (int)ceil_div(g.k_stages, splits);
+  gs.splits = (int)ceil_div(g.k_stages, gs.ks_per_split);     // no empty split
+  gs.slice_rows = (int)slice_rows;
+  gs.d = sk.ws;
+  gs.ldd = g.cols;
+  gs.out_f32 = 1;
+  gs.bias = nullptr;
+  gs.vec_ok = gs.tma_ok = (reinterpret_cast<uintptr_t>(sk.ws) % 16 == 0) && ((g.cols * 4) % 16 == 0);
+  int rc = launch_gemm<kFmt, kBN, kCtas>(p_codes, q_codes, gs, kbytes, clusters, stream);
+  if (rc != FP4T_OK) return rc;
+  const int64_t total = (int64_t)g.rows * g.cols;
+  cudaLaunchConfig_t cfg = {};
+  const int64_t blocks = ceil_div(total, 256);
+  cfg.gridDim = dim3((unsigned)(blocks > 148 * 8 ? 148 * 8 : blocks), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  pdl_attribute(&attr);
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FP4T_CUDA(cudaLaunchKernelEx(&cfg, splitk_finalize_kernel, static_cast<const float*>(sk.ws), gs.splits,
+                               slice_rows * (int64_t)g.cols, g.d, g.out_f32, g.ldd, g.rows, g.cols, g.bias));
+  return FP4T_OK;
+}
+
 template <int kFmt, int kCtas>
 int launch_best_width(const void* p_codes, const void* q_codes, const GemmParams& g, int64_t kbytes, int64_t cols,
-                      cudaStream_t stream, const char* name) {
+                      const SplitK& sk, cudaStream_t stream, const char* name) {
   const int c256 = max_clusters<kFmt, 256, kCtas>(), c128 = max_clusters<kFmt, 128, kCtas>();
   if (c256 <= 0 || c128 <= 0) {
     set_error("%s: the kernel cannot be resident on this device", name);
@@ -897,16 +977,17 @@ int launch_best_width(const void* p_codes, const void* q_codes, const GemmParams
     // that every SM pulls; 64-column tiles double the number of CTAs at work
     const int c64 = max_clusters<kFmt, 64, 1>();
     const double k64 = c64 > 0 ? (double)ceil_div(cm * ceil_div(cols, 64), c64) * (128.0 + 64.0) : 1e30;
-    if (k64 < k128 && k64 < k256) return launch_gemm<kFmt, 64, 1>(p_codes, q_codes, g, kbytes, c64, stream);
+    if (k64 < k128 && k64 < k256) return launch_maybe_split<kFmt, 64, 1>(p_codes, q_codes, g, kbytes, c64, sk, stream);
   }
-  if (k256 <= k128) return launch_gemm<kFmt, 256, kCtas>(p_codes, q_codes, g, kbytes, c256, stream);
-  return launch_gemm<kFmt, 128, kCtas>(p_codes, q_codes, g, kbytes, c128, stream);
+  if (k256 <= k128) return launch_maybe_split<kFmt, 256, kCtas>(p_codes, q_codes, g, kbytes, c256, sk, stream);
+  return launch_maybe_split<kFmt, 128, kCtas>(p_codes, q_codes, g, kbytes, c128, sk, stream);
 }
 
 template <int kFmt>
 int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf, const void* bias,
                   void* d, int d_dtype, int64_t ldd, int64_t rows, int64_t cols, int64_t k, int32_t* status,
-                  cudaStream_t stream, int out_q = 0, void* d_sf = nullptr) {
+                  cudaStream_t stream, int out_q = 0, void* d_sf = nullptr, void* workspace = nullptr,
+                  int64_t workspace_bytes = 0) {
   const char* name = out_q ? (kFmt == kNvfp4 ? "fp4t_gemm_nvfp4_qout" : "fp4t_gemm_mxfp8_qout")
                            : (kFmt == kNvfp4 ? "fp4t_gemm_nvfp4" : "fp4t_gemm_mxfp8");
   constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
@@ -958,6 +1039,9 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
   g.sched = sched_slot_for(stream);
   g.status = status;
   g.n_tiles = 0;
+  g.splits = 1;
+  g.ks_per_split = g.k_stages;
+  g.slice_rows = 0;
   g.out_q = out_q;
   g.d_sf = static_cast<uint8_t*>(d_sf);
   g.d_ntx = out_q ? (int)ceil_div(cols / (out_q == FP4T_QOUT_NVFP4 ? 16 : 32), 4) : 0;
@@ -970,8 +1054,14 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
   // CTA pairs whenever there are at least two 128-row tiles (FP4T_GEMM_1CTA=1 keeps the
   // single-CTA form, for comparisons).
   static const bool force_1cta = [] { const char* e = getenv("FP4T_GEMM_1CTA"); return e && e[0] == '1'; }();
-  if (g.m_tiles >= 2 && !force_1cta) return launch_best_width<kFmt, 2>(p_codes, q_codes, g, kbytes, cols, stream, name);
-  return launch_best_width<kFmt, 1>(p_codes, q_codes, g, kbytes, cols, stream, name);
+  SplitK sk;
+  if (workspace != nullptr && workspace_bytes > 0) {
+    FP4T_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0, "%s: the workspace must be 16-byte aligned", name);
+    sk.ws = workspace;
+    sk.ws_bytes = workspace_bytes;
+  }
+  if (g.m_tiles >= 2 && !force_1cta) return launch_best_width<kFmt, 2>(p_codes, q_codes, g, kbytes, cols, sk, stream, name);
+  return launch_best_width<kFmt, 1>(p_codes, q_codes, g, kbytes, cols, sk, stream, name);
 }
 
 }  // namespace
@@ -1012,4 +1102,34 @@ extern "C" int fp4t_gemm_mxfp8_qout(const void* p_codes, const void* p_sf, const
                                     int64_t rows, int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream) {
   return fp4t::gemm_dispatch<fp4t::kMxfp8>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d_codes, FP4T_DT_BF16, ldd, rows, cols,
                                            k, status, reinterpret_cast<cudaStream_t>(stream), out_fmt, d_sf);
+}
+
+// Largest output (elements) for which a split-K workspace is worth having: beyond it the
+// output's own tiles fill the machine.
+static const int64_t kSplitKMaxOutput = 1ll << 21;
+
+extern "C" int64_t fp4t_gemm_splitk_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0 || rows * cols > kSplitKMaxOutput) return 0;
+  const int64_t slice = (rows + 255) / 256 * 256 * cols * 4;
+  int64_t splits = (64ll << 20) / slice;          // at most 64 MiB
+  if (splits > 74) splits = 74;
+  return splits >= 2 ? splits * slice : 0;
+}
+
+extern "C" int fp4t_gemm_nvfp4_splitk(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                                      const void* bias_bf16, void* d, int d_dtype, int64_t ldd, int64_t rows,
+                                      int64_t cols, int64_t k, void* workspace, int64_t workspace_bytes,
+                                      int32_t* status, fp4t_stream_t stream) {
+  return fp4t::gemm_dispatch<fp4t::kNvfp4>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d, d_dtype, ldd, rows, cols, k,
+                                           status, reinterpret_cast<cudaStream_t>(stream), 0, nullptr, workspace,
+                                           workspace_bytes);
+}
+
+extern "C" int fp4t_gemm_mxfp8_splitk(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                                      const void* bias_bf16, void* d, int d_dtype, int64_t ldd, int64_t rows,
+                                      int64_t cols, int64_t k, void* workspace, int64_t workspace_bytes,
+                                      int32_t* status, fp4t_stream_t stream) {
+  return fp4t::gemm_dispatch<fp4t::kMxfp8>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d, d_dtype, ldd, rows, cols, k,
+                                           status, reinterpret_cast<cudaStream_t>(stream), 0, nullptr, workspace,
+                                           workspace_bytes);
 }

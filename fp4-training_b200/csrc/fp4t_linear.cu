@@ -12,7 +12,7 @@ struct Sections {
   int64_t xc, xsf, wc, wsf, xtc, xtsf, wtc, wtsf, total;      // forward workspace
 };
 struct BwdSections {
-  int64_t gc, gsf, gtc, gtsf, colsum, total;                  // backward workspace
+  int64_t gc, gsf, gtc, gtsf, colsum, splitk, splitk_bytes, total;   // backward workspace
 };
 
 inline int64_t code_bytes(int fmt, int64_t outer, int64_t k) { return fmt == 0 ? outer * (k / 2) : outer * k; }
@@ -32,7 +32,7 @@ Sections fwd_sections(int fmt, int64_t n, int64_t ic, int64_t oc) {
   s.total = o;
   return s;
 }
-BwdSections bwd_sections(int fmt, int64_t n, int64_t oc) {
+BwdSections bwd_sections(int fmt, int64_t n, int64_t oc, int64_t ic) {
   BwdSections s;
   int64_t o = 0;
   s.gc = o;     o += align256(code_bytes(fmt, n, oc));
@@ -40,6 +40,10 @@ BwdSections bwd_sections(int fmt, int64_t n, int64_t oc) {
   s.gtc = o;    o += align256(code_bytes(fmt, oc, n));
   s.gtsf = o;   o += align256(sf_bytes(fmt, oc, n));
   s.colsum = o; o += align256(oc * 4);
+  // fp32 slices for a split-K wgrad: dW [oc, ic] of a small layer has too few tiles for the
+  // machine while its K (the batch) is long
+  s.splitk_bytes = fp4t_gemm_splitk_workspace_bytes(oc, ic);
+  s.splitk = o; o += align256(s.splitk_bytes);
   s.total = o;
   return s;
 }
@@ -54,9 +58,9 @@ extern "C" int64_t fp4t_linear_workspace_bytes(int fmt, int64_t n, int64_t ic, i
   return fwd_sections(fmt, n, ic, oc).total;
 }
 
-extern "C" int64_t fp4t_linear_backward_workspace_bytes(int fmt, int64_t n, int64_t oc) {
-  if (fmt < 0 || fmt > 1 || n < 0 || oc < 0) return -1;
-  return bwd_sections(fmt, n, oc).total;
+extern "C" int64_t fp4t_linear_backward_workspace_bytes(int fmt, int64_t n, int64_t oc, int64_t ic) {
+  if (fmt < 0 || fmt > 1 || n < 0 || oc < 0 || ic < 0) return -1;
+  return bwd_sections(fmt, n, oc, ic).total;
 }
 
 extern "C" int fp4t_linear_forward(int fmt, const void* x, int x_dtype, int64_t n, int64_t ic, int64_t ldx,
@@ -102,7 +106,7 @@ extern "C" int fp4t_linear_backward(int fmt, const void* g, int g_dtype, int64_t
                    reinterpret_cast<uintptr_t>(fwd_workspace) % 256 == 0,
                "fp4t_linear_backward: workspaces must be 256-byte aligned");
   const Sections f = fwd_sections(fmt, n, ic, oc);
-  const BwdSections b = bwd_sections(fmt, n, oc);
+  const BwdSections b = bwd_sections(fmt, n, oc, ic);
   const uint8_t* fw = static_cast<const uint8_t*>(fwd_workspace);
   uint8_t* bw = static_cast<uint8_t*>(bwd_workspace);
   void* gc = dx ? bw + b.gc : nullptr;
@@ -126,12 +130,14 @@ extern "C" int fp4t_linear_backward(int fmt, const void* g, int g_dtype, int64_t
     return FP4T_ERR_UNSUPPORTED;
   }
   auto gemm = fmt == 0 ? fp4t_gemm_nvfp4 : fp4t_gemm_mxfp8;
+  auto gemm_splitk = fmt == 0 ? fp4t_gemm_nvfp4_splitk : fp4t_gemm_mxfp8_splitk;
   if (dx) {   // dX[n, ic] = dY[n, oc] . (W^T)[ic, oc]^T
     rc = gemm(gc, gsf, fw + f.wtc, fw + f.wtsf, nullptr, dx, out_dtype, lddx, n, ic, oc, status, stream);
     if (rc != FP4T_OK) return rc;
   }
   if (dw) {   // dW[oc, ic] = (dY^T)[oc, n] . (X^T)[ic, n]^T
-    rc = gemm(gtc, gtsf, fw + f.xtc, fw + f.xtsf, nullptr, dw, out_dtype, lddw, oc, ic, n, status, stream);
+    rc = gemm_splitk(gtc, gtsf, fw + f.xtc, fw + f.xtsf, nullptr, dw, out_dtype, lddw, oc, ic, n,
+                     b.splitk_bytes ? bw + b.splitk : nullptr, b.splitk_bytes, status, stream);
     if (rc != FP4T_OK) return rc;
   }
   return FP4T_OK;

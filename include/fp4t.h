@@ -251,6 +251,28 @@ FP4T_API int fp4t_gemm_mxfp8_qout(const void* p_codes, const void* p_sf, const v
                          int64_t rows, int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream);
 
 /*
+ * The GEMMs with an optional split-K workspace (caller-owned, 16-byte aligned, contents
+ * ignored and overwritten).  When the output has so few tiles that most SMs would idle -- the
+ * wgrad of a small layer over a long batch: dW 192 x 192 with K = 25600 is ONE tile -- the K loop
+ * is split over the idle SMs: every split writes its fp32 partial to a slice of the workspace and
+ * a small kernel adds the slices (+ bias) into d.  With a null or too small workspace, or a
+ * shape that fills the machine anyway, the call is exactly fp4t_gemm_*.
+ * fp4t_gemm_splitk_workspace_bytes(rows, cols) is the size that allows the full split (0 when
+ * the output is large enough not to need one).  The sum over splits is taken in a fixed order,
+ * so results are deterministic; they differ from the unsplit kernel's by fp32 summation order.
+ * No counterpart in the reference (cuBLASLt picks split-K kernels by itself).
+ */
+FP4T_API int64_t fp4t_gemm_splitk_workspace_bytes(int64_t rows, int64_t cols);
+FP4T_API int fp4t_gemm_nvfp4_splitk(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                           const void* bias_bf16, void* d, int d_dtype, int64_t ldd, int64_t rows, int64_t cols,
+                           int64_t k, void* workspace, int64_t workspace_bytes, int32_t* status,
+                           fp4t_stream_t stream);
+FP4T_API int fp4t_gemm_mxfp8_splitk(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                           const void* bias_bf16, void* d, int d_dtype, int64_t ldd, int64_t rows, int64_t cols,
+                           int64_t k, void* workspace, int64_t workspace_bytes, int32_t* status,
+                           fp4t_stream_t stream);
+
+/*
  * A whole linear layer per call.  fmt: 0 = NVFP4, 1 = MXFP8.
  *
  * fp4t_linear_forward quantizes W [oc, ic] and X [n, ic] (emitting the transposed operands of
@@ -261,7 +283,8 @@ FP4T_API int fp4t_gemm_mxfp8_qout(const void* p_codes, const void* p_sf, const v
  * fp4t_linear_backward quantizes dY [n, oc] once (stochastic rounding per sr_mode for NVFP4),
  * and computes any of dX [n, ic] = dY W, dW [oc, ic] = dY^T X and db [oc] = column sums of dY
  * (null pointers skip an output) from the forward workspace and a second workspace of
- * fp4t_linear_backward_workspace_bytes(fmt, n, oc) bytes.  Outputs are written in out_dtype.
+ * fp4t_linear_backward_workspace_bytes(fmt, n, oc, ic) bytes (it includes the fp32 slices of a
+ * split-K wgrad when dW is small).  Outputs are written in out_dtype.
  * Shape requirements are those of the quantizer and GEMM entry points (ic, oc multiples of the
  * block size; n % 32 == 0 for the transposed operands).
  *
@@ -269,7 +292,7 @@ FP4T_API int fp4t_gemm_mxfp8_qout(const void* p_codes, const void* p_sf, const v
  * Mxfp8MatMul.forward / .backward (custom/linear/mxfp8.py:27-85).
  */
 FP4T_API int64_t fp4t_linear_workspace_bytes(int fmt, int64_t n, int64_t ic, int64_t oc);
-FP4T_API int64_t fp4t_linear_backward_workspace_bytes(int fmt, int64_t n, int64_t oc);
+FP4T_API int64_t fp4t_linear_backward_workspace_bytes(int fmt, int64_t n, int64_t oc, int64_t ic);
 FP4T_API int fp4t_linear_forward(int fmt, const void* x, int x_dtype, int64_t n, int64_t ic, int64_t ldx,
                                  const void* w, int w_dtype, int64_t oc, int64_t ldw, const void* bias_bf16,
                                  void* y, int y_dtype, int64_t ldy, void* workspace, int keep,
