@@ -77,8 +77,10 @@ _colsum_scratch = {}
 
 def _scratch(dev, cols):
     """fp32 scratch of at least `cols` values on `dev` for the fused bias-gradient sums
-    (grown on demand, reused by every call on that device: calls are stream-ordered)."""
-    key = (dev.type, dev.index)
+    (grown on demand, reused by the calls of one stream, which are ordered)."""
+    # one buffer per (device, stream): calls on one stream are ordered, calls on different streams
+    # may overlap on the GPU and must not share the accumulator
+    key = (dev.type, dev.index, _lib.stream_ptr(dev))
     buf = _colsum_scratch.get(key)
     if buf is None or buf.numel() < cols:
         buf = torch.empty(max(cols, 4096), dtype=torch.float32, device=dev)

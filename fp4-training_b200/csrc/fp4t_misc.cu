@@ -52,6 +52,11 @@ int sched_slot_for(cudaStream_t stream) {
     cudaGetLastError();
     return -1;
   }
+  // cudaStreamPerThread is ONE handle value that stands for a different stream in every host
+  // thread: grids launched through it from two threads may run at the same time and must not
+  // share a counter.  (The legacy default stream, handle 0 or cudaStreamLegacy, is one stream.)
+  if (stream == cudaStreamPerThread) return -1;
+  if (stream == cudaStreamLegacy) stream = nullptr;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
   struct Key { int dev; cudaStream_t stream; };

@@ -623,18 +623,13 @@ __global__ void colsum_finalize_kernel(const float* __restrict__ colsum, void* _
   else static_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(colsum[c]);
 }
 
+// Argument checks of the quantizer entry points (no launch).  `name` is the entry point the
+// caller used, so that messages name it.
 template <int kFmt>
-int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, void* codes, void* sf,
-                   void* codes_t, void* sf_t, int sr_mode, const float* noise, const float* noise_t, uint64_t seed,
-                   float* colsum_scratch, void* bias_grad, int bias_grad_dtype, cudaStream_t stream);
-
-template <int kFmt>
-int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
-                      void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
-                      const float* noise, const float* noise_t, uint64_t seed, float* colsum,
-                      cudaStream_t stream) {
+int quantize_check(const char* name, const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                   const void* codes, const void* sf, const void* codes_t, const void* sf_t, int sr_mode,
+                   const float* noise, const float* noise_t) {
   constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
-  const char* name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4" : "fp4t_quantize_mxfp8";
   FP4T_REQUIRE(x != nullptr, "%s: x is null", name);
   FP4T_REQUIRE(x_dtype == FP4T_DT_BF16 || x_dtype == FP4T_DT_F32, "%s: x_dtype must be bf16 or f32", name);
   FP4T_REQUIRE(rows >= 0 && cols >= 0 && ld >= cols, "%s: bad shape rows=%lld cols=%lld ld=%lld", name,
@@ -648,6 +643,20 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   if (sr_mode == FP4T_SR_NOISE) {
     FP4T_REQUIRE((codes == nullptr || noise != nullptr) && (codes_t == nullptr || noise_t != nullptr),
                  "%s: sr_mode NOISE needs a noise tensor for every requested output", name);
+  }
+  return FP4T_OK;
+}
+
+template <int kFmt>
+int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                      void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
+                      const float* noise, const float* noise_t, uint64_t seed, float* colsum,
+                      cudaStream_t stream, const char* name = nullptr) {
+  constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
+  if (name == nullptr) name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4" : "fp4t_quantize_mxfp8";
+  {
+    const int rc = quantize_check<kFmt>(name, x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise, noise_t);
+    if (rc != FP4T_OK) return rc;
   }
   if (rows == 0 || cols == 0) return FP4T_OK;
 
@@ -734,12 +743,16 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
 template <int kFmt>
 int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, void* codes, void* sf,
                    void* codes_t, void* sf_t, int sr_mode, const float* noise, const float* noise_t, uint64_t seed,
-                   float* colsum_scratch, void* bias_grad, int bias_grad_dtype, cudaStream_t stream) {
-  const char* name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4_bgrad" : "fp4t_quantize_mxfp8_bgrad";
+                   float* colsum_scratch, void* bias_grad, int bias_grad_dtype, cudaStream_t stream,
+                   const char* name = nullptr) {
+  if (name == nullptr) name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4_bgrad" : "fp4t_quantize_mxfp8_bgrad";
   FP4T_REQUIRE(colsum_scratch != nullptr && bias_grad != nullptr, "%s: scratch and bias_grad must be given", name);
   FP4T_REQUIRE(reinterpret_cast<uintptr_t>(colsum_scratch) % 4 == 0, "%s: scratch must be 4-byte aligned", name);
   FP4T_REQUIRE(bias_grad_dtype == FP4T_DT_BF16 || bias_grad_dtype == FP4T_DT_F32, "%s: bad bias_grad dtype", name);
-  FP4T_REQUIRE(cols >= 0, "%s: negative cols", name);
+  {   // every argument is checked before the first kernel is enqueued
+    const int rc = quantize_check<kFmt>(name, x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise, noise_t);
+    if (rc != FP4T_OK) return rc;
+  }
   if (cols == 0) return FP4T_OK;
   {
     cudaLaunchConfig_t cfg = {};
@@ -754,7 +767,7 @@ int quantize_bgrad(const void* x, int x_dtype, int64_t rows, int64_t cols, int64
   }
   if (rows > 0) {
     const int rc = quantize_dispatch<kFmt>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise,
-                                           noise_t, seed, colsum_scratch, stream);
+                                           noise_t, seed, colsum_scratch, stream, name);
     if (rc != FP4T_OK) return rc;
   }
   {
@@ -845,7 +858,7 @@ extern "C" int fp4t_quantize_nvfp4_bgrad_static(const void* x, int x_dtype, int6
   if (rc != FP4T_OK) return rc;
   return fp4t::quantize_bgrad<fp4t::kNvfp4>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, noise,
                                             noise_t, seed, scratch, bias_grad, bias_grad_dtype,
-                                            reinterpret_cast<cudaStream_t>(stream));
+                                            reinterpret_cast<cudaStream_t>(stream), "fp4t_quantize_nvfp4_bgrad_static");
 }
 
 extern "C" int fp4t_quantize_nvfp4(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,

@@ -59,7 +59,7 @@ def quant_pair(fmt, t, want_row, want_t, sr=False, bias_grad_dtype=None):
 def grad_quant(fmt, grad_Y, need_dx, need_dw, need_db, sr):
     """Quantize dY for dgrad / wgrad and, if asked, take the bias gradient in the same pass.
     -> (codes, sf, codes_t, sf_t, grad_b or None)."""
-    if need_db and (need_dx or need_dw):
+    if need_db and need_dw:      # the column sums ride on the transposed pass
         return quant_pair(fmt, grad_Y, need_dx, need_dw, sr=sr, bias_grad_dtype=grad_Y.dtype)
     out = quant_pair(fmt, grad_Y, need_dx, need_dw, sr=sr) if (need_dx or need_dw) else (None,) * 4
     return (*out, grad_Y.sum(dim=0) if need_db else None)

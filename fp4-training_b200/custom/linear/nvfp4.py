@@ -86,12 +86,19 @@ class Nvfp4Matmul(torch.autograd.Function):
         else:
             Wtc, Wtsf, Xtc, Xtsf, W, X = ctx.saved_tensors
             need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+            # Where the fused kernel could not emit the transposed operand (its row count is a
+            # multiple of 16 but not of 32) the reference's own sequence serves: materialise the
+            # transpose and quantize it row-wise (custom/linear/nvfp4.py:59,74-75).
             if need_dx and Wtc is None:
-                _, _, Wtc, Wtsf = F.quant_pair("nvfp4", W, False, True)
+                Wtc, Wtsf, _, _ = F.quant_pair("nvfp4", W.T.contiguous(), True, False)
             if need_dw and Xtc is None:
-                _, _, Xtc, Xtsf = F.quant_pair("nvfp4", X, False, True)
+                Xtc, Xtsf, _, _ = F.quant_pair("nvfp4", X.T.contiguous(), True, False)
             need_db = ctx.has_bias and ctx.needs_input_grad[2]
-            Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, need_dw, need_db, sr=True)
+            if need_dw and not F.can_transpose(grad_Y):
+                Gc, Gsf, _, _, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, False, need_db, sr=True)
+                Gtc, Gtsf, _, _ = F.quant_pair("nvfp4", grad_Y.T.contiguous(), True, False, sr=True)
+            else:
+                Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, need_dw, need_db, sr=True)
             if need_dx:
                 grad_X = F.gemm("nvfp4", Gc, Gsf, Wtc, Wtsf, None, grad_Y.dtype)
             if need_dw:
