@@ -37,6 +37,8 @@ _SIGNATURES = {
                                             ctypes.c_int, _c_vp, _c_vp, ctypes.c_uint64, _c_vp]),
     "fp4t_quantize_mxfp8": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
                                             _c_vp]),
+    "fp4t_quantize_nvfp4_gelu": (ctypes.c_int, [_c_vp, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
+    "fp4t_quantize_mxfp8_gelu": (ctypes.c_int, [_c_vp, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
     "fp4t_quantize_nvfp4_bgrad": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
                                                   ctypes.c_int, _c_vp, _c_vp, ctypes.c_uint64, _c_vp, _c_vp, ctypes.c_int,
                                                   _c_vp]),

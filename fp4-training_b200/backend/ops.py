@@ -164,6 +164,42 @@ def quantize_mxfp8(x, want_row=True, want_t=False, bias_grad_dtype=None):
     return _quantize("mxfp8", x, want_row, want_t, SR_NONE, None, None, 0, bias_grad_dtype)
 
 
+def quantize_gelu(fmt, x, want_row=True, want_t=False):
+    """Quantization of GELU(x) for a bf16 pre-activation x, the activation applied inside the
+    quantizer (its bf16 result is never materialised).  -> (codes, sf, codes_t, sf_t)."""
+    if x.ndim != 2:
+        raise ValueError("Input tensor must be 2D for block quantization")
+    _need_cuda(x)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("the fused GELU quantizer takes a bfloat16 pre-activation")
+    blk = NVFP4_BLOCK if fmt == "nvfp4" else MXFP8_BLOCK
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, cols = x.shape
+    if want_row and cols % blk:
+        raise ValueError(f"row-wise {fmt} quantization needs columns to be a multiple of {blk}")
+    if want_t and rows % 32:
+        raise ValueError(f"transposed {fmt} quantization needs rows to be a multiple of 32")
+    dev = x.device
+    codes = sf = codes_t = sf_t = None
+    with _on_device(dev):
+        if want_row:
+            codes, sf = _alloc_q(rows, cols, blk, fmt == "nvfp4", dev)
+        if want_t:
+            codes_t, sf_t = _alloc_q(cols, rows, blk, fmt == "nvfp4", dev)
+        if rows == 0 or cols == 0:
+            return codes, sf, codes_t, sf_t
+        _bind_status(dev)
+        fn = _lib.lib().fp4t_quantize_nvfp4_gelu if fmt == "nvfp4" else _lib.lib().fp4t_quantize_mxfp8_gelu
+        rc = fn(_lib.ptr(x), rows, cols, x.stride(0), _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                _lib.stream_ptr(dev))
+        if rc == -3:
+            raise NotImplementedError(_lib.lib().fp4t_last_error().decode("utf-8", "replace"))
+        _lib.check(rc, f"fp4t_quantize_{fmt}_gelu")
+        LAUNCHES["quantize"] += 1
+    return codes, sf, codes_t, sf_t
+
+
 def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None, split_k=True):
     _need_cuda(p_codes, p_sf, q_codes, q_sf, bias)
     rows, cols = p_codes.shape[0], q_codes.shape[0]

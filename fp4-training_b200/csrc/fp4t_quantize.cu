@@ -358,7 +358,19 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
 // {next tile, CTAs done} per stream slot; zero between launches (the last CTA to run dry resets them)
 __device__ unsigned int g_quant_sched[2 * kSchedSlots];
 
-template <int kFmt, int kSr, bool kColsum>
+// GELU of eight bf16 values, as torch's CUDA kernel computes it for bf16 tensors: in fp32,
+// x * 0.5 * (1 + erf(x * sqrt(1/2))), rounded to bf16.
+__device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t w) {
+  const float a = __uint_as_float(w << 16), b = __uint_as_float(w & 0xFFFF0000u);
+  const float ga = (a * 0.5f) * (1.0f + erff(a * 0.70710678118654752440f));
+  const float gb = (b * 0.5f) * (1.0f + erff(b * 0.70710678118654752440f));
+  const __nv_bfloat162 h = __floats2bfloat162_rn(ga, gb);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// kPre: 0 = quantize the input as it is; 1 = quantize GELU(input) (the activation is applied to
+// the tile in shared memory, so its bf16 result never travels through HBM).
+template <int kFmt, int kSr, bool kColsum, int kPre = 0>
 __global__ void __launch_bounds__(kQThreads, 2)
 quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, const int tiles_x,
                     const int num_tiles, const int sched, int32_t* status) {
@@ -458,6 +470,19 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
     c.scale_tab = scale_tab;
     c.seed = seed;
     c.tid = tid;
+    if (kPre == 1) {
+      // 2048 16-byte vectors per tile, eight per thread; parts of the tile outside the tensor
+      // were filled with zeros and GELU(0) = 0, so they stay zeros
+      uint4* tile_v = reinterpret_cast<uint4*>(gen + stage * kQTileBytes);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint4 v = tile_v[tid + i * kQComputeThreads];
+        v.x = gelu_bf16x2(v.x); v.y = gelu_bf16x2(v.y); v.z = gelu_bf16x2(v.z); v.w = gelu_bf16x2(v.w);
+        tile_v[tid + i * kQComputeThreads] = v;
+      }
+      fence_async_smem();        // these writes are ordered before the TMA refill of the stage
+      named_barrier_compute();
+    }
     const bool interior = c.row0 + kTile <= p.rows && c.col0 + kTile <= p.cols;
     if (interior) {
       if (want_row) row_pass<kFmt, kSr, false>(p, c);
@@ -651,7 +676,7 @@ template <int kFmt>
 int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
                       void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
                       const float* noise, const float* noise_t, uint64_t seed, float* colsum,
-                      cudaStream_t stream, const char* name = nullptr) {
+                      cudaStream_t stream, const char* name = nullptr, int pre_op = 0) {
   constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
   if (name == nullptr) name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4" : "fp4t_quantize_mxfp8";
   {
@@ -674,6 +699,10 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
                     (codes_t == nullptr || reinterpret_cast<uintptr_t>(codes_t) % 16 == 0) &&
                     (sf == nullptr || reinterpret_cast<uintptr_t>(sf) % 16 == 0) &&
                     (sf_t == nullptr || reinterpret_cast<uintptr_t>(sf_t) % 16 == 0);
+  if (pre_op != 0 && (!fast || colsum != nullptr || sr_mode != FP4T_SR_NONE)) {
+    set_error("%s: the fused activation needs bf16 input with 16-byte aligned rows and outputs, round-to-nearest", name);
+    return FP4T_ERR_UNSUPPORTED;
+  }
   if (!fast || (colsum != nullptr && codes_t == nullptr)) {
     // column sums ride on the transposed pass of the tiled kernel; otherwise a plain kernel adds them
     if (colsum != nullptr) {
@@ -705,9 +734,10 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   const int grid = num_tiles < 2 * sms ? num_tiles : 2 * sms;
   int32_t* status = current_status_word();
   const int sched = sched_slot_for(stream);
-#define FP4T_LAUNCH_Q2(FMT, SR, CS)                                                                        \
+#define FP4T_LAUNCH_Q2(FMT, SR, CS) FP4T_LAUNCH_Q3(FMT, SR, CS, 0)
+#define FP4T_LAUNCH_Q3(FMT, SR, CS, PRE)                                                                   \
   do {                                                                                                     \
-    auto kern = quantize_tma_kernel<FMT, SR, CS>;                                                          \
+    auto kern = quantize_tma_kernel<FMT, SR, CS, PRE>;                                                     \
     FP4T_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QCfg<FMT>::kSmemBytes)); \
     cudaLaunchConfig_t cfg = {};                                                                           \
     cfg.gridDim = dim3((unsigned)grid, 1, 1);                                                              \
@@ -725,7 +755,10 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
     if (p.colsum != nullptr) FP4T_LAUNCH_Q2(FMT, SR, true); \
     else FP4T_LAUNCH_Q2(FMT, SR, false);        \
   } while (0)
-  if (kFmt == kMxfp8) {
+  if (pre_op == 1) {
+    if (kFmt == kMxfp8) FP4T_LAUNCH_Q3(kMxfp8, FP4T_SR_NONE, false, 1);
+    else FP4T_LAUNCH_Q3(kNvfp4, FP4T_SR_NONE, false, 1);
+  } else if (kFmt == kMxfp8) {
     FP4T_LAUNCH_Q(kMxfp8, FP4T_SR_NONE);
   } else if (sr_mode == FP4T_SR_NONE) {
     FP4T_LAUNCH_Q(kNvfp4, FP4T_SR_NONE);
@@ -736,6 +769,7 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   }
 #undef FP4T_LAUNCH_Q
 #undef FP4T_LAUNCH_Q2
+#undef FP4T_LAUNCH_Q3
   FP4T_CUDA(cudaGetLastError());
   return FP4T_OK;
 }
@@ -876,4 +910,18 @@ extern "C" int fp4t_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int
   return fp4t::quantize_dispatch<fp4t::kMxfp8>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t,
                                                FP4T_SR_NONE, nullptr, nullptr, 0, nullptr,
                                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fp4t_quantize_nvfp4_gelu(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld, void* codes, void* sf,
+                                        void* codes_t, void* sf_t, fp4t_stream_t stream) {
+  return fp4t::quantize_dispatch<fp4t::kNvfp4>(x_bf16, FP4T_DT_BF16, rows, cols, ld, codes, sf, codes_t, sf_t, FP4T_SR_NONE,
+                                               nullptr, nullptr, 0, nullptr, reinterpret_cast<cudaStream_t>(stream),
+                                               "fp4t_quantize_nvfp4_gelu", 1);
+}
+
+extern "C" int fp4t_quantize_mxfp8_gelu(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld, void* codes, void* sf,
+                                        void* codes_t, void* sf_t, fp4t_stream_t stream) {
+  return fp4t::quantize_dispatch<fp4t::kMxfp8>(x_bf16, FP4T_DT_BF16, rows, cols, ld, codes, sf, codes_t, sf_t, FP4T_SR_NONE,
+                                               nullptr, nullptr, 0, nullptr, reinterpret_cast<cudaStream_t>(stream),
+                                               "fp4t_quantize_mxfp8_gelu", 1);
 }

@@ -105,3 +105,49 @@ def layer_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db, sr):
             return _ops.linear_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db, _ops.SR_NOISE, noise, noise_t)
         return _ops.linear_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db, _ops.SR_HASH, seed=Q._next_seed())
     return _ops.linear_backward(fmt, grad_Y, ws, ic, need_dx, need_dw, need_db)
+
+
+class GeluQuantizedMatmul(torch.autograd.Function):
+    """Y = GELU(P) W^T + b with GELU applied inside the quantizer of the activation operand
+    (`fp4t_quantize_*_gelu`): the pre-activation P is read once and GELU(P) is never written as
+    a bf16 tensor.  Values are those of `linear(F.gelu(P))` with the stock quantizer table, bit
+    for bit (the kernel evaluates torch's own GELU formula and rounds to bf16 before quantizing).
+    Backward: dY is quantized once, dH = dY W and dW = dY^T GELU(P) come from the saved transposed
+    codes, and dP = dH * GELU'(P) is torch's gelu_backward on the saved pre-activation."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx, P, W, b, fmt, sr):
+        if P.ndim != 2 or W.ndim != 2:
+            raise ValueError("Input tensor must be 2D")
+        P = P.contiguous()
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        Xc, Xsf, Xtc, Xtsf = _ops.quantize_gelu(fmt, P, True, need_dw)
+        Wc, Wsf, Wtc, Wtsf = quant_pair(fmt, W, True, need_dx)
+        Y = gemm(fmt, Xc, Xsf, Wc, Wsf, b, P.dtype)
+        ctx.fmt, ctx.sr, ctx.has_bias = fmt, sr, b is not None
+        ctx.save_for_backward(P, Wtc, Wtsf, Xtc, Xtsf)
+        return Y
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_Y):
+        P, Wtc, Wtsf, Xtc, Xtsf = ctx.saved_tensors
+        grad_Y = grad_Y.contiguous()
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        need_db = ctx.has_bias and ctx.needs_input_grad[2]
+        Gc, Gsf, Gtc, Gtsf, grad_b = grad_quant(ctx.fmt, grad_Y, need_dx, need_dw, need_db, sr=ctx.sr)
+        grad_P = grad_W = None
+        if need_dx:
+            grad_H = gemm(ctx.fmt, Gc, Gsf, Wtc, Wtsf, None, grad_Y.dtype)
+            grad_P = torch.ops.aten.gelu_backward(grad_H, P.to(grad_H.dtype))
+        if need_dw:
+            grad_W = gemm(ctx.fmt, Gtc, Gtsf, Xtc, Xtsf, None, grad_Y.dtype)
+        return grad_P, grad_W, grad_b, None, None
+
+
+def gelu_linear(module, pre, fmt, sr):
+    """module(GELU(pre)) through GeluQuantizedMatmul; `pre` may have leading dims."""
+    shape = pre.shape
+    out = GeluQuantizedMatmul.apply(pre.reshape(-1, shape[-1]), module.weight, module.bias, fmt, sr)
+    return out.view(shape[:-1] + (module.out_features,))

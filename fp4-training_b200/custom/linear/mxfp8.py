@@ -131,3 +131,10 @@ class CublasltMxfp8Linear(CustomLinear):
 
     def forward(self, input):
         return flatten_apply(self, Mxfp8MatMul.apply, input, self.quantizers)
+
+    def forward_gelu(self, pre_activation):
+        """self(GELU(pre_activation)) with the activation fused into the quantizer of the input
+        operand (no bf16 GELU output in HBM).  Needs the stock quantizer table."""
+        if not F.is_stock(self.quantizers, STOCK):
+            return self.forward(torch.nn.functional.gelu(pre_activation))
+        return F.gelu_linear(self, pre_activation, "mxfp8", False)

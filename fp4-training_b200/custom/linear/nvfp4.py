@@ -46,6 +46,12 @@ class Nvfp4Matmul(torch.autograd.Function):
             raise ValueError("Input tensor must be 2D for nvfp4 quantization")
         X = X.contiguous()
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if need_dw and X.shape[0] % 32:
+            # wgrad contracts over the batch: its K must be a multiple of 32 (FP4 rows of 16-byte
+            # multiples).  Said here, not in the middle of the backward pass.
+            raise ValueError(f"nvfp4 weight gradients need the flattened batch ({X.shape[0]}) to be a multiple of 32")
+        if need_dx and W.shape[0] % 32:
+            raise ValueError(f"nvfp4 input gradients need out_features ({W.shape[0]}) to be a multiple of 32")
         ctx.layer_call = F.layer_call_ok("nvfp4", X, W, need_dx, need_dw)
         if ctx.layer_call:      # one C call for the layer; the workspace holds the backward operands
             Y, ws = F.layer_forward("nvfp4", X, W, b, need_dx, need_dw)
@@ -86,19 +92,12 @@ class Nvfp4Matmul(torch.autograd.Function):
         else:
             Wtc, Wtsf, Xtc, Xtsf, W, X = ctx.saved_tensors
             need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-            # Where the fused kernel could not emit the transposed operand (its row count is a
-            # multiple of 16 but not of 32) the reference's own sequence serves: materialise the
-            # transpose and quantize it row-wise (custom/linear/nvfp4.py:59,74-75).
             if need_dx and Wtc is None:
-                Wtc, Wtsf, _, _ = F.quant_pair("nvfp4", W.T.contiguous(), True, False)
+                _, _, Wtc, Wtsf = F.quant_pair("nvfp4", W, False, True)
             if need_dw and Xtc is None:
-                Xtc, Xtsf, _, _ = F.quant_pair("nvfp4", X.T.contiguous(), True, False)
+                _, _, Xtc, Xtsf = F.quant_pair("nvfp4", X, False, True)
             need_db = ctx.has_bias and ctx.needs_input_grad[2]
-            if need_dw and not F.can_transpose(grad_Y):
-                Gc, Gsf, _, _, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, False, need_db, sr=True)
-                Gtc, Gtsf, _, _ = F.quant_pair("nvfp4", grad_Y.T.contiguous(), True, False, sr=True)
-            else:
-                Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, need_dw, need_db, sr=True)
+            Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, need_dw, need_db, sr=True)
             if need_dx:
                 grad_X = F.gemm("nvfp4", Gc, Gsf, Wtc, Wtsf, None, grad_Y.dtype)
             if need_dw:
@@ -127,3 +126,10 @@ class CublasltNvfp4Linear(CustomLinear):
 
     def forward(self, input):
         return flatten_apply(self, Nvfp4Matmul.apply, input, self.quantizers)
+
+    def forward_gelu(self, pre_activation):
+        """self(GELU(pre_activation)) with the activation fused into the quantizer of the input
+        operand (no bf16 GELU output in HBM).  Needs the stock quantizer table."""
+        if not F.is_stock(self.quantizers, STOCK):
+            return self.forward(torch.nn.functional.gelu(pre_activation))
+        return F.gelu_linear(self, pre_activation, "nvfp4", True)

@@ -57,9 +57,10 @@ class AttentionBlock(nn.Module):
 
 
 class TransformerBlock(nn.Module):
-    def __init__(self, E, F, H, dropout=0.1, impl="torch"):
+    def __init__(self, E, F, H, dropout=0.1, impl="torch", fuse_gelu=False):
         super().__init__()
         self.E, self.F, self.H, self.impl = E, F, H, impl
+        self.fuse_gelu = fuse_gelu      # an addition: see forward()
         self.attn = AttentionBlock(E, H, dropout, impl=impl)
         linear = LINEAR_IMPL[impl]
         self.ffn = nn.ModuleDict({
@@ -74,6 +75,13 @@ class TransformerBlock(nn.Module):
     def forward(self, x):
         hidden = self.attn(x)
         residual = hidden           # the FFN residual is the attention output
-        for layer in self.ffn.values():
+        ffn = self.ffn
+        act_dropout_off = (not self.training) or ffn["act_dropout"].p == 0.0
+        if self.fuse_gelu and act_dropout_off and hasattr(ffn["down_proj"], "forward_gelu"):
+            # GELU goes into the quantizer of down_proj's input operand: same values, one
+            # kernel and one HBM round trip less (only where no dropout sits between them)
+            hidden = ffn["dropout"](ffn["down_proj"].forward_gelu(ffn["up_proj"](ffn["preln"](hidden))))
+            return residual + hidden
+        for layer in ffn.values():
             hidden = layer(hidden)
         return residual + hidden

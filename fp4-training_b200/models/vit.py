@@ -1,6 +1,7 @@
-"""TinyViT classifier (reference: models/vit.py:12-87) with one addition: `depth`, the
+"""TinyViT classifier (reference: models/vit.py:12-87) with two additions: `depth`, the
 number of transformer blocks (the reference builds exactly one; depth=1 reproduces its
-module tree, parameter names included)."""
+module tree, parameter names included), and `fuse_gelu`, which lets the MLP's GELU run inside
+the quantizer of the down-projection's input where no dropout sits between them."""
 import torch
 from torch import nn
 
@@ -9,7 +10,7 @@ from .transformer_block import TransformerBlock
 
 class TinyViT(nn.Module):
     def __init__(self, img_size=28, patch_size=7, in_chans=1, num_classes=10, embed_dim=64, num_heads=4,
-                 mlp_ratio=2.0, linear_impl="torch", depth=1):
+                 mlp_ratio=2.0, linear_impl="torch", depth=1, fuse_gelu=False):
         super().__init__()
         self.linear_impl = linear_impl
         assert img_size % patch_size == 0, "patch_size must divide img_size exactly"
@@ -21,7 +22,8 @@ class TinyViT(nn.Module):
         nn.init.trunc_normal_(self.cls_token, std=0.02)
 
         def block():
-            return TransformerBlock(E=embed_dim, F=int(embed_dim * mlp_ratio), H=num_heads, impl=linear_impl)
+            return TransformerBlock(E=embed_dim, F=int(embed_dim * mlp_ratio), H=num_heads, impl=linear_impl,
+                                    fuse_gelu=fuse_gelu)
 
         self.depth = depth
         self.encoder = block() if depth == 1 else nn.Sequential(*[block() for _ in range(depth)])

@@ -150,6 +150,21 @@ FP4T_API int fp4t_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int64
                         fp4t_stream_t stream);
 
 /*
+ * The quantizers with the activation in front of them fused in: the output is the quantization
+ * of GELU(x) -- as torch computes it for a bf16 tensor: in fp32, x * 0.5 * (1 + erf(x / sqrt 2)),
+ * rounded to bf16 -- without that bf16 tensor ever being written to or read from HBM.  x is the
+ * bf16 pre-activation [rows, cols] (16-byte aligned rows); outputs as fp4t_quantize_*.
+ *
+ * Replaces `act` followed by the quantizer call inside `down_proj` in the reference's MLP
+ * (models/transformer_block.py:45-52 -> custom/linear/nvfp4.py:28-33) where no dropout sits
+ * between them (inference, or dropout 0).
+ */
+FP4T_API int fp4t_quantize_nvfp4_gelu(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld,
+                             void* codes, void* sf, void* codes_t, void* sf_t, fp4t_stream_t stream);
+FP4T_API int fp4t_quantize_mxfp8_gelu(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld,
+                             void* codes, void* sf, void* codes_t, void* sf_t, fp4t_stream_t stream);
+
+/*
  * The same quantizers with the bias gradient fused in: while the kernel walks dY for the
  * transposed operand it also accumulates the column sums of dY, so
  *   bias_grad[c] = sum_r x[r, c]      (bf16 or fp32, selected by bias_grad_dtype)
