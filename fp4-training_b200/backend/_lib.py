@@ -37,6 +37,10 @@ _SIGNATURES = {
                                             ctypes.c_int, _c_vp, _c_vp, ctypes.c_uint64, _c_vp]),
     "fp4t_quantize_mxfp8": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
                                             _c_vp]),
+    "fp4t_quantize_nvfp4_scaled": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
+                                                   ctypes.c_int, ctypes.c_uint64, ctypes.c_float, _c_vp]),
+    "fp4t_quantize_nvfp4_rht": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
+                                                ctypes.c_uint32, ctypes.c_float, _c_vp]),
     "fp4t_quantize_nvfp4_gelu": (ctypes.c_int, [_c_vp, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
     "fp4t_quantize_mxfp8_gelu": (ctypes.c_int, [_c_vp, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
     "fp4t_quantize_nvfp4_bgrad": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp,
@@ -60,6 +64,8 @@ _SIGNATURES = {
     "fp4t_gemm_splitk_workspace_bytes": (_c_i64, [_c_i64, _c_i64]),
     "fp4t_gemm_nvfp4_splitk": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,
                                                _c_i64, _c_vp, _c_i64, _c_vp, _c_vp]),
+    "fp4t_gemm_nvfp4_scaled": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,
+                                               _c_i64, ctypes.c_float, _c_vp, _c_i64, _c_vp, _c_vp]),
     "fp4t_gemm_mxfp8_splitk": (ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64,
                                                _c_i64, _c_vp, _c_i64, _c_vp, _c_vp]),
     "fp4t_linear_forward": (ctypes.c_int, [ctypes.c_int, _c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, ctypes.c_int,

@@ -164,6 +164,55 @@ def quantize_mxfp8(x, want_row=True, want_t=False, bias_grad_dtype=None):
     return _quantize("mxfp8", x, want_row, want_t, SR_NONE, None, None, 0, bias_grad_dtype)
 
 
+def quantize_nvfp4_scaled(x, tensor_scale, want_row=True, want_t=False, sr=SR_NONE, seed=0, rht_signs=None):
+    """NVFP4 block quantization of x * tensor_scale (the second, per-tensor scale level), with
+    an optional random Hadamard transform of each 16-block (rht_signs: 16-bit sign mask).
+    -> (codes, sf, codes_t, sf_t); the operands describe x * tensor_scale, so a GEMM of two of
+    them takes alpha = 1 / (t_p * t_q) (gemm_nvfp4(..., alpha=...))."""
+    if x.ndim != 2:
+        raise ValueError("Input tensor must be 2D for block quantization")
+    _need_cuda(x)
+    if not (tensor_scale > 0.0 and tensor_scale < 3.0e38):
+        raise ValueError("tensor_scale must be positive and finite")
+    if rht_signs is not None and sr != SR_NONE:
+        raise ValueError("the Hadamard-transformed quantizer rounds to nearest")
+    if sr not in (SR_NONE, SR_HASH):
+        raise ValueError("the scaled quantizer takes round-to-nearest or in-kernel stochastic rounding")
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        x = x.to(torch.float32)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, cols = x.shape
+    if want_row and cols % NVFP4_BLOCK:
+        raise ValueError("row-wise nvfp4 quantization needs columns to be a multiple of 16")
+    if want_t and rows % 32:
+        raise ValueError("transposed nvfp4 quantization needs rows to be a multiple of 32")
+    dev = x.device
+    codes = sf = codes_t = sf_t = None
+    with _on_device(dev):
+        if want_row:
+            codes, sf = _alloc_q(rows, cols, NVFP4_BLOCK, True, dev)
+        if want_t:
+            codes_t, sf_t = _alloc_q(cols, rows, NVFP4_BLOCK, True, dev)
+        if rows == 0 or cols == 0:
+            return codes, sf, codes_t, sf_t
+        _bind_status(dev)
+        L = _lib.lib()
+        if rht_signs is None:
+            rc = L.fp4t_quantize_nvfp4_scaled(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                              _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t), int(sr),
+                                              ctypes.c_uint64(seed & (2 ** 64 - 1)), float(tensor_scale),
+                                              _lib.stream_ptr(dev))
+            _lib.check(rc, "fp4t_quantize_nvfp4_scaled")
+        else:
+            rc = L.fp4t_quantize_nvfp4_rht(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                           _lib.ptr(codes), _lib.ptr(sf), _lib.ptr(codes_t), _lib.ptr(sf_t),
+                                           int(rht_signs) & 0xFFFF, float(tensor_scale), _lib.stream_ptr(dev))
+            _lib.check(rc, "fp4t_quantize_nvfp4_rht")
+        LAUNCHES["quantize"] += 1
+    return codes, sf, codes_t, sf_t
+
+
 def quantize_gelu(fmt, x, want_row=True, want_t=False):
     """Quantization of GELU(x) for a bf16 pre-activation x, the activation applied inside the
     quantizer (its bf16 result is never materialised).  -> (codes, sf, codes_t, sf_t)."""
@@ -200,7 +249,7 @@ def quantize_gelu(fmt, x, want_row=True, want_t=False):
     return codes, sf, codes_t, sf_t
 
 
-def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None, split_k=True):
+def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None, split_k=True, alpha=1.0):
     _need_cuda(p_codes, p_sf, q_codes, q_sf, bias)
     rows, cols = p_codes.shape[0], q_codes.shape[0]
     kbytes = p_codes.shape[1]
@@ -219,7 +268,15 @@ def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None, split_k=
             return out
         L = _lib.lib()
         ws_bytes = L.fp4t_gemm_splitk_workspace_bytes(rows, cols) if (split_k and k >= 2048) else 0
-        if ws_bytes > 0:      # a small output over a long K: let the idle SMs share the K loop
+        if alpha != 1.0:
+            if fmt != "nvfp4":
+                raise ValueError("alpha (per-tensor operand scales) is an NVFP4 option")
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes > 0 else None
+            rc = L.fp4t_gemm_nvfp4_scaled(_lib.ptr(p_codes), _lib.ptr(p_sf), _lib.ptr(q_codes), _lib.ptr(q_sf),
+                                          _lib.ptr(bias), _lib.ptr(out), _lib.dtype_code(out.dtype), out.stride(0),
+                                          rows, cols, k, float(alpha), _lib.ptr(ws), max(ws_bytes, 0),
+                                          _lib.ptr(status_word(dev)), _lib.stream_ptr(dev))
+        elif ws_bytes > 0:      # a small output over a long K: let the idle SMs share the K loop
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             fn = L.fp4t_gemm_nvfp4_splitk if fmt == "nvfp4" else L.fp4t_gemm_mxfp8_splitk
             rc = fn(_lib.ptr(p_codes), _lib.ptr(p_sf), _lib.ptr(q_codes), _lib.ptr(q_sf), _lib.ptr(bias),
@@ -235,10 +292,11 @@ def _gemm(fmt, p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out=None, split_k=
     return out
 
 
-def gemm_nvfp4(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None, split_k=True):
-    """D[rows, cols] = P . Q^T (+bias); P/Q packed E2M1 codes [outer, K/2].  split_k=False keeps
-    a small-output / long-K product on the unsplit kernel (one fixed accumulation order)."""
-    return _gemm("nvfp4", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out, split_k)
+def gemm_nvfp4(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None, split_k=True, alpha=1.0):
+    """D[rows, cols] = alpha * P . Q^T (+bias); P/Q packed E2M1 codes [outer, K/2].  split_k=False
+    keeps a small-output / long-K product on the unsplit kernel (one fixed accumulation order);
+    alpha undoes per-tensor operand scales (quantize_nvfp4_scaled)."""
+    return _gemm("nvfp4", p_codes, p_sf, q_codes, q_sf, bias, out_dtype, out, split_k, alpha)
 
 
 def gemm_mxfp8(p_codes, p_sf, q_codes, q_sf, bias=None, out_dtype=torch.bfloat16, out=None, split_k=True):

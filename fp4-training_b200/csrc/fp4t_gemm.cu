@@ -82,6 +82,7 @@ struct GemmParams {
   int out_q;        // 0: bf16 / fp32 output; FP4T_QOUT_MXFP8 / FP4T_QOUT_NVFP4: block-quantized output
   uint8_t* d_sf;    // scale bytes of the quantized output (128x4 tile layout of logical [rows, cols / block])
   int d_ntx;        // scale tiles along the columns of the quantized output
+  float alpha;      // the accumulator is multiplied by alpha before the bias (undoes per-tensor operand scales)
   int32_t* status;
 };
 
@@ -227,6 +228,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& g, const int row, 
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (g.alpha != 1.0f) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
+    }
     if (g.bias != nullptr) {
       if (g.vec_ok && col0 + 32 <= g.cols) {
         const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
@@ -297,6 +302,10 @@ __device__ __forceinline__ void emit_chunk(const GemmParams& g, const CUtensorMa
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (g.alpha != 1.0f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
+  }
   if (g.bias != nullptr) {
     if (g.vec_ok && col0 + 32 <= g.cols) {
       const uint4* bp = reinterpret_cast<const uint4*>(g.bias + col0);
@@ -366,6 +375,10 @@ __device__ __forceinline__ void quant_chunk(const GemmParams& g, const int row, 
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (g.alpha != 1.0f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= g.alpha;
+  }
   if (g.bias != nullptr) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(g.bias[col0 + j]);
@@ -987,11 +1000,12 @@ template <int kFmt>
 int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf, const void* bias,
                   void* d, int d_dtype, int64_t ldd, int64_t rows, int64_t cols, int64_t k, int32_t* status,
                   cudaStream_t stream, int out_q = 0, void* d_sf = nullptr, void* workspace = nullptr,
-                  int64_t workspace_bytes = 0) {
-  const char* name = out_q ? (kFmt == kNvfp4 ? "fp4t_gemm_nvfp4_qout" : "fp4t_gemm_mxfp8_qout")
+                  int64_t workspace_bytes = 0, float alpha = 1.0f, const char* name_override = nullptr) {
+  const char* name = name_override ? name_override : out_q ? (kFmt == kNvfp4 ? "fp4t_gemm_nvfp4_qout" : "fp4t_gemm_mxfp8_qout")
                            : (kFmt == kNvfp4 ? "fp4t_gemm_nvfp4" : "fp4t_gemm_mxfp8");
   constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
   FP4T_REQUIRE(p_codes && p_sf && q_codes && q_sf && d, "%s: null pointer", name);
+  FP4T_REQUIRE(alpha == alpha && alpha - alpha == 0.0f, "%s: alpha must be finite", name);
   if (out_q) {
     FP4T_REQUIRE(out_q == FP4T_QOUT_MXFP8 || out_q == FP4T_QOUT_NVFP4, "%s: out_fmt must be FP4T_QOUT_MXFP8 or FP4T_QOUT_NVFP4", name);
     FP4T_REQUIRE(d_sf != nullptr, "%s: d_sf is null", name);
@@ -1043,6 +1057,7 @@ int gemm_dispatch(const void* p_codes, const void* p_sf, const void* q_codes, co
   g.ks_per_split = g.k_stages;
   g.slice_rows = 0;
   g.out_q = out_q;
+  g.alpha = alpha;
   g.d_sf = static_cast<uint8_t*>(d_sf);
   g.d_ntx = out_q ? (int)ceil_div(cols / (out_q == FP4T_QOUT_NVFP4 ? 16 : 32), 4) : 0;
   if (out_q) {
@@ -1132,4 +1147,13 @@ extern "C" int fp4t_gemm_mxfp8_splitk(const void* p_codes, const void* p_sf, con
   return fp4t::gemm_dispatch<fp4t::kMxfp8>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d, d_dtype, ldd, rows, cols, k,
                                            status, reinterpret_cast<cudaStream_t>(stream), 0, nullptr, workspace,
                                            workspace_bytes);
+}
+
+extern "C" int fp4t_gemm_nvfp4_scaled(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                                      const void* bias_bf16, void* d, int d_dtype, int64_t ldd, int64_t rows,
+                                      int64_t cols, int64_t k, float alpha, void* workspace, int64_t workspace_bytes,
+                                      int32_t* status, fp4t_stream_t stream) {
+  return fp4t::gemm_dispatch<fp4t::kNvfp4>(p_codes, p_sf, q_codes, q_sf, bias_bf16, d, d_dtype, ldd, rows, cols, k,
+                                           status, reinterpret_cast<cudaStream_t>(stream), 0, nullptr, workspace,
+                                           workspace_bytes, alpha, "fp4t_gemm_nvfp4_scaled");
 }

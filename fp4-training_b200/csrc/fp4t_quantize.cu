@@ -33,6 +33,8 @@ struct QParams {
   const float* noise_t;
   float* colsum;   // optional fp32 [cols] accumulator of column sums (transposed pass only)
   uint64_t seed;
+  float tscale, tscale_inv;   // per-tensor scale applied before block quantization (kPre == 2), and its reciprocal
+  uint32_t rht_signs;         // generic path: bit 16 set = random Hadamard transform of each 16-block, bits 0..15 the signs
   const uint64_t* seed_dev;   // optional device word added (times an odd constant) to `seed` when the kernel runs
   int ntx_row;  // scale tiles along k for the row-wise output
   int ntx_col;  // ... for the transposed output
@@ -116,7 +118,7 @@ struct TileCtx {
 // ---- row-wise pass: a thread owns one whole block of a row (16 or 32 elements) ----------
 // 8 (NVFP4) or 4 (MXFP8) threads cover a tile row, so the block's abs-max needs no shuffle and
 // the scale work (table look-up, scale byte, packed operands) is paid once per block.
-template <int kFmt, int kSr, bool kEdge>
+template <int kFmt, int kSr, bool kEdge, bool kTs = false>
 __device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
   using C = QCfg<kFmt>;
   constexpr int kTpr = kTile / C::kBlk;                // threads per tile row
@@ -161,12 +163,14 @@ __device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
   if (kFmt == kNvfp4) {
     float s[kIts], rcp[kIts];
 #pragma unroll
-    for (int it = 0; it < kIts; ++it) nvfp4_scale_from_table(c.scale_tab, amax[it], s[it], rcp[it]);
+    for (int it = 0; it < kIts; ++it) nvfp4_scale_from_table(c.scale_tab, kTs ? amax[it] * p.tscale : amax[it], s[it], rcp[it]);
     uint32_t packed[kIts][2];
 #pragma unroll
     for (int it = 0; it < kIts; ++it) {
       const int64_t gr = c.row0 + it * kRowsPerIt + r_base;
-      const uint64_t rcp2 = pack2(rcp[it], rcp[it]), neg2 = pack2(-s[it], -s[it]);
+      // with a (power of two) tensor scale t the block scale s belongs to x t: x t / s = x / (s / t)
+      const float se = kTs ? s[it] * p.tscale_inv : s[it], re = kTs ? rcp[it] * p.tscale : rcp[it];
+      const uint64_t rcp2 = pack2(re, re), neg2 = pack2(-se, -se);
 #pragma unroll
       for (int v = 0; v < 2; ++v) {
         float y[8];
@@ -226,7 +230,7 @@ __device__ __forceinline__ void row_pass(const QParams& p, const TileCtx& c) {
 }
 
 // ---- transposed pass: a thread handles 2 adjacent columns x 32 rows --------------------
-template <int kFmt, int kSr, bool kEdge, bool kColsum>
+template <int kFmt, int kSr, bool kEdge, bool kColsum, bool kTs = false>
 __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
   const int cp = c.tid & 63, q = c.tid >> 6;
   const int64_t gr0 = c.row0 + q * 32, gcA = c.col0 + 2 * cp;
@@ -256,12 +260,13 @@ __device__ __forceinline__ void col_pass(const QParams& p, const TileCtx& c) {
       }
       const float amA = fmaxf(fmaxf(mA[0], mA[1]), fmaxf(mA[2], mA[3]));
       const float amB = fmaxf(fmaxf(mB[0], mB[1]), fmaxf(mB[2], mB[3]));
-      nvfp4_scale_from_table(c.scale_tab, amA, sA[h], rA[h]);
-      nvfp4_scale_from_table(c.scale_tab, amB, sB[h], rB[h]);
+      nvfp4_scale_from_table(c.scale_tab, kTs ? amA * p.tscale : amA, sA[h], rA[h]);
+      nvfp4_scale_from_table(c.scale_tab, kTs ? amB * p.tscale : amB, sB[h], rB[h]);
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const uint64_t rcp2 = pack2(rA[h], rB[h]), neg2 = pack2(-sA[h], -sB[h]);
+      const uint64_t rcp2 = kTs ? pack2(rA[h] * p.tscale, rB[h] * p.tscale) : pack2(rA[h], rB[h]);
+      const uint64_t neg2 = kTs ? pack2(-sA[h] * p.tscale_inv, -sB[h] * p.tscale_inv) : pack2(-sA[h], -sB[h]);
 #pragma unroll
       for (int g8 = 0; g8 < 2; ++g8) {
         float yA[8], yB[8];
@@ -369,7 +374,8 @@ __device__ __forceinline__ uint32_t gelu_bf16x2(uint32_t w) {
 }
 
 // kPre: 0 = quantize the input as it is; 1 = quantize GELU(input) (the activation is applied to
-// the tile in shared memory, so its bf16 result never travels through HBM).
+// the tile in shared memory, so its bf16 result never travels through HBM); 2 = quantize
+// input x tensor scale (a power of two, folded into the block scale's operands).
 template <int kFmt, int kSr, bool kColsum, int kPre = 0>
 __global__ void __launch_bounds__(kQThreads, 2)
 quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, const int tiles_x,
@@ -484,12 +490,13 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
       named_barrier_compute();
     }
     const bool interior = c.row0 + kTile <= p.rows && c.col0 + kTile <= p.cols;
+    constexpr bool kTs = kPre == 2;
     if (interior) {
-      if (want_row) row_pass<kFmt, kSr, false>(p, c);
-      if (want_col) col_pass<kFmt, kSr, false, kColsum>(p, c);
+      if (want_row) row_pass<kFmt, kSr, false, kTs>(p, c);
+      if (want_col) col_pass<kFmt, kSr, false, kColsum, kTs>(p, c);
     } else {
-      if (want_row) row_pass<kFmt, kSr, true>(p, c);
-      if (want_col) col_pass<kFmt, kSr, true, kColsum>(p, c);
+      if (want_row) row_pass<kFmt, kSr, true, kTs>(p, c);
+      if (want_col) col_pass<kFmt, kSr, true, kColsum, kTs>(p, c);
     }
 
     // the tile is consumed: hand the stage back to the producer
@@ -555,9 +562,30 @@ __global__ void quantize_generic_kernel(const QParams p, const int transposed, c
     for (int j = 0; j < kBlk; ++j) {
       const int64_t i = kb * kBlk + j;
       const int64_t idx = transposed ? i * p.ld + o : o * p.ld + i;
-      f[j] = (float)x[idx];
-      amax = fmaxf(amax, fabsf(f[j]));
+      f[j] = (float)x[idx] * p.tscale;
     }
+    if (kFmt == kNvfp4 && (p.rht_signs & 0x10000u)) {
+      // random Hadamard transform of the block: signs, then the 16-point fast Walsh-Hadamard
+      // butterflies (strides 1, 2, 4, 8), then 1/4 -- an orthogonal map, so two operands
+      // transformed with the same signs keep their dot products
+#pragma unroll
+      for (int j = 0; j < kBlk; ++j) f[j] = ((p.rht_signs >> (j & 15)) & 1u) ? -f[j] : f[j];
+#pragma unroll
+      for (int h = 1; h < 16; h <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if ((j & h) == 0) {
+            const float a = f[j], b = f[j + h];
+            f[j] = __fadd_rn(a, b);
+            f[j + h] = __fsub_rn(a, b);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kBlk; ++j) f[j] *= 0.25f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBlk; ++j) amax = fmaxf(amax, fabsf(f[j]));
     if (kFmt == kNvfp4) {
       const float s = nvfp4_scale(amax);
       uint32_t word = 0;
@@ -676,7 +704,8 @@ template <int kFmt>
 int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
                       void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode,
                       const float* noise, const float* noise_t, uint64_t seed, float* colsum,
-                      cudaStream_t stream, const char* name = nullptr, int pre_op = 0) {
+                      cudaStream_t stream, const char* name = nullptr, int pre_op = 0, float tscale = 1.0f,
+                      uint32_t rht_signs = 0) {
   constexpr int kBlk = kFmt == kNvfp4 ? 16 : 32;
   if (name == nullptr) name = kFmt == kNvfp4 ? "fp4t_quantize_nvfp4" : "fp4t_quantize_mxfp8";
   {
@@ -690,10 +719,18 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   p.codes = static_cast<uint8_t*>(codes); p.sf = static_cast<uint8_t*>(sf);
   p.codes_t = static_cast<uint8_t*>(codes_t); p.sf_t = static_cast<uint8_t*>(sf_t);
   p.noise = noise; p.noise_t = noise_t; p.seed = seed; p.seed_dev = seed_offset_word(); p.colsum = colsum;
+  p.tscale = tscale; p.tscale_inv = 1.0f / tscale; p.rht_signs = rht_signs;
+  const bool options = tscale != 1.0f || rht_signs != 0;
+  const bool options_ok = !options || (kFmt == kNvfp4 && tscale > 0.0f && tscale < 3.0e38f);
+  FP4T_REQUIRE(options_ok, "%s: tensor_scale (NVFP4 only) must be positive and finite", name);
+  int mant_exp = 0;
+  const bool pow2 = frexpf(tscale, &mant_exp) == 0.5f;
   p.ntx_row = (int)ceil_div(ceil_div(cols, kBlk), 4);
   p.ntx_col = (int)ceil_div(ceil_div(rows, kBlk), 4);
 
-  const bool fast = x_dtype == FP4T_DT_BF16 && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+  // the tiled kernel's exact-division shortcut holds for bf16 inputs times a power of two; any
+  // other tensor scale, and the Hadamard transform, take the general kernel
+  const bool fast = x_dtype == FP4T_DT_BF16 && pow2 && rht_signs == 0 && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
                     (ld % 8 == 0) && (cols % 8 == 0) &&
                     (codes == nullptr || reinterpret_cast<uintptr_t>(codes) % 16 == 0) &&
                     (codes_t == nullptr || reinterpret_cast<uintptr_t>(codes_t) % 16 == 0) &&
@@ -758,6 +795,18 @@ int quantize_dispatch(const void* x, int x_dtype, int64_t rows, int64_t cols, in
   if (pre_op == 1) {
     if (kFmt == kMxfp8) FP4T_LAUNCH_Q3(kMxfp8, FP4T_SR_NONE, false, 1);
     else FP4T_LAUNCH_Q3(kNvfp4, FP4T_SR_NONE, false, 1);
+  } else if (kFmt == kNvfp4 && tscale != 1.0f) {
+    if (sr_mode == FP4T_SR_NOISE) {
+      set_error("%s: a tensor scale combines with round-to-nearest or in-kernel stochastic rounding", name);
+      return FP4T_ERR_UNSUPPORTED;
+    }
+    if (sr_mode == FP4T_SR_NONE) {
+      if (p.colsum != nullptr) FP4T_LAUNCH_Q3(kNvfp4, FP4T_SR_NONE, true, 2);
+      else FP4T_LAUNCH_Q3(kNvfp4, FP4T_SR_NONE, false, 2);
+    } else {
+      if (p.colsum != nullptr) FP4T_LAUNCH_Q3(kNvfp4, FP4T_SR_HASH, true, 2);
+      else FP4T_LAUNCH_Q3(kNvfp4, FP4T_SR_HASH, false, 2);
+    }
   } else if (kFmt == kMxfp8) {
     FP4T_LAUNCH_Q(kMxfp8, FP4T_SR_NONE);
   } else if (sr_mode == FP4T_SR_NONE) {
@@ -924,4 +973,24 @@ extern "C" int fp4t_quantize_mxfp8_gelu(const void* x_bf16, int64_t rows, int64_
   return fp4t::quantize_dispatch<fp4t::kMxfp8>(x_bf16, FP4T_DT_BF16, rows, cols, ld, codes, sf, codes_t, sf_t, FP4T_SR_NONE,
                                                nullptr, nullptr, 0, nullptr, reinterpret_cast<cudaStream_t>(stream),
                                                "fp4t_quantize_mxfp8_gelu", 1);
+}
+
+extern "C" int fp4t_quantize_nvfp4_scaled(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, void* codes,
+                                          void* sf, void* codes_t, void* sf_t, int sr_mode, uint64_t seed,
+                                          float tensor_scale, fp4t_stream_t stream) {
+  return fp4t::quantize_dispatch<fp4t::kNvfp4>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, sr_mode, nullptr,
+                                               nullptr, seed, nullptr, reinterpret_cast<cudaStream_t>(stream),
+                                               "fp4t_quantize_nvfp4_scaled", 0, tensor_scale, 0);
+}
+
+extern "C" int fp4t_quantize_nvfp4_rht(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, void* codes,
+                                       void* sf, void* codes_t, void* sf_t, uint32_t sign_mask, float tensor_scale,
+                                       fp4t_stream_t stream) {
+  if (codes_t != nullptr && rows % 16 != 0) {
+    fp4t::set_error("fp4t_quantize_nvfp4_rht: the transposed output needs rows %% 16 == 0");
+    return FP4T_ERR_ARG;
+  }
+  return fp4t::quantize_dispatch<fp4t::kNvfp4>(x, x_dtype, rows, cols, ld, codes, sf, codes_t, sf_t, FP4T_SR_NONE, nullptr,
+                                               nullptr, 0, nullptr, reinterpret_cast<cudaStream_t>(stream),
+                                               "fp4t_quantize_nvfp4_rht", 0, tensor_scale, (sign_mask & 0xFFFFu) | 0x10000u);
 }

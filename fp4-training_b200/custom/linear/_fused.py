@@ -65,9 +65,17 @@ def grad_quant(fmt, grad_Y, need_dx, need_dw, need_db, sr):
     return (*out, grad_Y.sum(dim=0) if need_db else None)
 
 
-def gemm(fmt, p, p_sf, q, q_sf, bias, out_dtype):
-    fn = _ops.gemm_nvfp4 if fmt == "nvfp4" else _ops.gemm_mxfp8
-    return fn(p, p_sf, q, q_sf, bias, out_dtype)
+def grad_quant_scaled(grad_Y, tensor_scale, need_dx, need_dw):
+    """NVFP4 operands of dY * tensor_scale with in-kernel stochastic rounding -> (codes, sf, codes_t, sf_t)."""
+    if not (need_dx or need_dw):
+        return (None,) * 4
+    return _ops.quantize_nvfp4_scaled(grad_Y, tensor_scale, need_dx, need_dw, sr=_ops.SR_HASH, seed=Q._next_seed())
+
+
+def gemm(fmt, p, p_sf, q, q_sf, bias, out_dtype, alpha=1.0):
+    if fmt == "nvfp4":
+        return _ops.gemm_nvfp4(p, p_sf, q, q_sf, bias, out_dtype, alpha=alpha)
+    return _ops.gemm_mxfp8(p, p_sf, q, q_sf, bias, out_dtype)
 
 
 def can_transpose(t) -> bool:

@@ -32,10 +32,13 @@ class Nvfp4Matmul(torch.autograd.Function):
 
     @staticmethod
     @custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
-    def forward(ctx, X, W, b, quant: OrderedDict):
+    def forward(ctx, X, W, b, quant: OrderedDict, grad_scale: float = 1.0):
         ctx.quant = quant
+        ctx.grad_scale = float(grad_scale)
         ctx.has_bias = b is not None
         ctx.fused = F.is_stock(quant, STOCK)
+        if ctx.grad_scale != 1.0 and not ctx.fused:
+            raise ValueError("grad_tensor_scale needs the stock quantizer table")
         if not ctx.fused:
             Wq, sW = quant['1A'](W)
             Xq, sX = quant['1B'](X)
@@ -52,7 +55,7 @@ class Nvfp4Matmul(torch.autograd.Function):
             raise ValueError(f"nvfp4 weight gradients need the flattened batch ({X.shape[0]}) to be a multiple of 32")
         if need_dx and W.shape[0] % 32:
             raise ValueError(f"nvfp4 input gradients need out_features ({W.shape[0]}) to be a multiple of 32")
-        ctx.layer_call = F.layer_call_ok("nvfp4", X, W, need_dx, need_dw)
+        ctx.layer_call = F.layer_call_ok("nvfp4", X, W, need_dx, need_dw) and ctx.grad_scale == 1.0
         if ctx.layer_call:      # one C call for the layer; the workspace holds the backward operands
             Y, ws = F.layer_forward("nvfp4", X, W, b, need_dx, need_dw)
             ctx.ic = X.shape[1]
@@ -88,7 +91,7 @@ class Nvfp4Matmul(torch.autograd.Function):
             need_db = ctx.has_bias and ctx.needs_input_grad[2]
             grad_X, grad_W, grad_b = F.layer_backward("nvfp4", grad_Y, ws, ctx.ic, ctx.needs_input_grad[0],
                                                       ctx.needs_input_grad[1], need_db, sr=True)
-            return grad_X, grad_W, grad_b, None
+            return grad_X, grad_W, grad_b, None, None
         else:
             Wtc, Wtsf, Xtc, Xtsf, W, X = ctx.saved_tensors
             need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
@@ -97,22 +100,36 @@ class Nvfp4Matmul(torch.autograd.Function):
             if need_dw and Xtc is None:
                 _, _, Xtc, Xtsf = F.quant_pair("nvfp4", X, False, True)
             need_db = ctx.has_bias and ctx.needs_input_grad[2]
-            Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, need_dw, need_db, sr=True)
+            t = ctx.grad_scale
+            if t != 1.0:     # second scale level on dY: quantize dY * t, give 1/t back in the GEMM epilogue
+                Gc, Gsf, Gtc, Gtsf = F.grad_quant_scaled(grad_Y, t, need_dx, need_dw)
+                grad_b = grad_Y.sum(dim=0) if need_db else None
+            else:
+                Gc, Gsf, Gtc, Gtsf, grad_b = F.grad_quant("nvfp4", grad_Y, need_dx, need_dw, need_db, sr=True)
             if need_dx:
-                grad_X = F.gemm("nvfp4", Gc, Gsf, Wtc, Wtsf, None, grad_Y.dtype)
+                grad_X = F.gemm("nvfp4", Gc, Gsf, Wtc, Wtsf, None, grad_Y.dtype, alpha=1.0 / t)
             if need_dw:
-                grad_W = F.gemm("nvfp4", Gtc, Gtsf, Xtc, Xtsf, None, grad_Y.dtype)
-            return grad_X, grad_W, grad_b, None
+                grad_W = F.gemm("nvfp4", Gtc, Gtsf, Xtc, Xtsf, None, grad_Y.dtype, alpha=1.0 / t)
+            return grad_X, grad_W, grad_b, None, None
         if ctx.has_bias and ctx.needs_input_grad[2]:
             grad_b = grad_Y.sum(dim=0)
-        return grad_X, grad_W, grad_b, None
+        return grad_X, grad_W, grad_b, None, None
 
 
 class CublasltNvfp4Linear(CustomLinear):
-    """`nn.Linear` drop-in whose three GEMMs run in NVFP4 on tcgen05."""
+    """`nn.Linear` drop-in whose three GEMMs run in NVFP4 on tcgen05.
 
-    def __init__(self, *args, **kwargs):
+    `grad_tensor_scale` (default 1, i.e. the reference's one-level recipe) is a per-tensor scale
+    on the gradient operand: dY * grad_tensor_scale is what gets block-quantized, and the dgrad
+    and wgrad GEMMs multiply their accumulators by its reciprocal.  A power of two keeps the
+    quantizer on its tiled kernel.  It lifts gradients whose blocks sit below the smallest
+    UE4M3 block scale (amax < 6 * 2^-9) back into the range the block scale can express."""
+
+    grad_tensor_scale = 1.0
+
+    def __init__(self, *args, grad_tensor_scale: float = 1.0, **kwargs):
         super().__init__(*args, **kwargs)
+        self.grad_tensor_scale = float(grad_tensor_scale)
         self._init_quantizers()
 
     @classmethod
@@ -125,7 +142,7 @@ class CublasltNvfp4Linear(CustomLinear):
         self.quantizers = OrderedDict(STOCK)   # all row-wise: every GEMM is K-major on both sides
 
     def forward(self, input):
-        return flatten_apply(self, Nvfp4Matmul.apply, input, self.quantizers)
+        return flatten_apply(self, Nvfp4Matmul.apply, input, self.quantizers, self.grad_tensor_scale)
 
     def forward_gelu(self, pre_activation):
         """self(GELU(pre_activation)) with the activation fused into the quantizer of the input

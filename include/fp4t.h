@@ -165,6 +165,36 @@ FP4T_API int fp4t_quantize_mxfp8_gelu(const void* x_bf16, int64_t rows, int64_t 
                              void* codes, void* sf, void* codes_t, void* sf_t, fp4t_stream_t stream);
 
 /*
+ * NVFP4 with a second, per-tensor scale level (the two-level recipe the reference lists as a
+ * TODO in its README's "Features to Add" and that its quantizer, custom/quantize.py:100-137,
+ * leaves at one level): the block quantization is applied to x * tensor_scale, so a tensor whose
+ * magnitudes sit below the reach of the UE4M3 block scale (smallest value 2^-9, i.e. blocks
+ * with amax < 6 * 2^-9 lose resolution, gradients late in training) is lifted into range first.
+ * Codes and block scales then describe x * tensor_scale; the product of two such operands is
+ * brought back by fp4t_gemm_nvfp4_scaled's alpha = 1 / (tensor_scale_p * tensor_scale_q).
+ * A power-of-two tensor_scale with bf16 input runs on the tiled kernel (the scale folds into the
+ * block-scale arithmetic exactly); any other positive value takes the general kernel.
+ * sr_mode: FP4T_SR_NONE or FP4T_SR_HASH.  tensor_scale = 1 gives fp4t_quantize_nvfp4 bit for bit.
+ */
+FP4T_API int fp4t_quantize_nvfp4_scaled(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                               void* codes, void* sf, void* codes_t, void* sf_t, int sr_mode, uint64_t seed,
+                               float tensor_scale, fp4t_stream_t stream);
+
+/*
+ * NVFP4 with a random Hadamard transform of every 16-element block in front of the block
+ * quantization (outlier spreading; the other recipe step the reference's README lists as to
+ * be added): block b of the quantized axis becomes H16 . diag(signs) . b / 4, with the signs
+ * from bits 0..15 of sign_mask (bit j set = element j negated) and H16 the Sylvester-ordered
+ * Hadamard matrix.  The map is orthogonal, so a GEMM of two operands transformed with the same
+ * sign_mask along K equals the GEMM of the untransformed operands up to quantization error.
+ * The row-wise output transforms blocks along the columns, the transposed output blocks along
+ * the rows (rows % 16 == 0).  Round-to-nearest-even; runs on the general kernel.
+ */
+FP4T_API int fp4t_quantize_nvfp4_rht(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                            void* codes, void* sf, void* codes_t, void* sf_t, uint32_t sign_mask,
+                            float tensor_scale, fp4t_stream_t stream);
+
+/*
  * The same quantizers with the bias gradient fused in: while the kernel walks dY for the
  * transposed operand it also accumulates the column sums of dY, so
  *   bias_grad[c] = sum_r x[r, c]      (bf16 or fp32, selected by bias_grad_dtype)
@@ -264,6 +294,16 @@ FP4T_API int fp4t_gemm_nvfp4_qout(const void* p_codes, const void* p_sf, const v
 FP4T_API int fp4t_gemm_mxfp8_qout(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
                          const void* bias_bf16, void* d_codes, void* d_sf, int out_fmt, int64_t ldd,
                          int64_t rows, int64_t cols, int64_t k, int32_t* status, fp4t_stream_t stream);
+
+/*
+ * fp4t_gemm_nvfp4 with D = alpha * (P . Q^T) + bias: alpha undoes the per-tensor scales of
+ * operands made by fp4t_quantize_nvfp4_scaled (alpha = 1 / (t_p * t_q)).  workspace may be null
+ * (or point at fp4t_gemm_splitk_workspace_bytes(rows, cols) bytes to allow the split-K form).
+ */
+FP4T_API int fp4t_gemm_nvfp4_scaled(const void* p_codes, const void* p_sf, const void* q_codes, const void* q_sf,
+                           const void* bias_bf16, void* d, int d_dtype, int64_t ldd, int64_t rows,
+                           int64_t cols, int64_t k, float alpha, void* workspace, int64_t workspace_bytes,
+                           int32_t* status, fp4t_stream_t stream);
 
 /*
  * The GEMMs with an optional split-K workspace (caller-owned, 16-byte aligned, contents

@@ -226,6 +226,40 @@ def nvfp4_quantize(x: torch.Tensor, noise_row=None, want_t: bool = False, noise_
     return out
 
 
+def hadamard16_blocks(x: torch.Tensor, sign_mask: int) -> torch.Tensor:
+    """Random Hadamard transform of every 16-element block along the last dim: element j of a
+    block is negated when bit j of sign_mask is set, then the Sylvester-ordered 16-point
+    Walsh-Hadamard butterflies run with strides 1, 2, 4, 8 (pairs (j, j+h) -> (a+b, a-b), fp32),
+    then the block is multiplied by 1/4 (H16 / 4 is orthogonal).  This recipe step is not in
+    the reference (its README lists it under features to add); the definition is this
+    framework's own and the CUDA quantizer follows it operation for operation."""
+    r, c = x.shape
+    v = x.to(torch.float32).reshape(r, c // 16, 16).clone()
+    signs = torch.tensor([-1.0 if (sign_mask >> j) & 1 else 1.0 for j in range(16)], dtype=torch.float32,
+                         device=x.device)
+    v = v * signs
+    for h in (1, 2, 4, 8):
+        w = v.reshape(r, c // 16, 16 // (2 * h), 2, h)
+        a, b = w[..., 0, :], w[..., 1, :]
+        v = torch.stack((a + b, a - b), dim=-2).reshape(r, c // 16, 16)
+    return (v * 0.25).reshape(r, c)
+
+
+def nvfp4_quantize_scaled(x: torch.Tensor, tensor_scale: float, want_t: bool = False, rht_signs=None):
+    """Two-level NVFP4: the block quantization of fp32(x) * tensor_scale (round-to-nearest),
+    optionally with the 16-block Hadamard transform in front of it.  Same outputs as
+    nvfp4_quantize.  Not in the reference (one scale level, custom/quantize.py:72-76)."""
+    def prep(t):
+        t = t.to(torch.float32) * torch.full((), tensor_scale, dtype=torch.float32, device=t.device)
+        return hadamard16_blocks(t, rht_signs) if rht_signs is not None else t
+    codes, sb = nvfp4_quantize_rowwise(prep(x))
+    out = {"codes": pack_fp4_pairs(codes), "sf": swizzle_rowwise(sb), "sf_logical": sb}
+    if want_t:
+        ct, sbt = nvfp4_quantize_rowwise(prep(x.t().contiguous()))
+        out.update({"codes_t": pack_fp4_pairs(ct), "sf_t": swizzle_rowwise(sbt), "sf_t_logical": sbt})
+    return out
+
+
 def nvfp4_dequant(codes: torch.Tensor, sbytes: torch.Tensor) -> torch.Tensor:
     """Unpacked codes [R, C] + logical E4M3 scale bytes [R, C/16] -> fp32 [R, C]."""
     v = e2m1_decode(codes)
