@@ -135,10 +135,12 @@ def test_hadamard_quantizer_bit_exact(ops, dtype, rows, cols):
     ops.check_status()
 
 
-def test_hadamard_keeps_the_product_and_spreads_outliers(ops):
+def test_hadamard_keeps_the_product(ops):
     """Both operands transformed with the same signs along K: the GEMM still approximates the
-    untransformed product, and with one large outlier per block more accurately than without
-    the transform (the outlier no longer sets the scale for 15 small neighbours)."""
+    untransformed product, with an error of the same order as the untransformed operands give.
+    (A 16-point transform inside 16-element scale blocks does not lower the Frobenius error --
+    on one 40-sigma outlier per block it is 0.15 against 0.12 -- its use is to decorrelate the
+    rounding error from the data, as recipes that transform the wgrad operands do.)"""
     n, k, m = 256, 1024, 256
     g = torch.Generator().manual_seed(11)
     a = torch.randn(n, k, generator=g)
@@ -154,8 +156,7 @@ def test_hadamard_keeps_the_product_and_spreads_outliers(ops):
     rht = ops.gemm_nvfp4(ah, ahsf, bh, bhsf, None, torch.float32)
     e_plain = orc.rel_frobenius(plain.cpu(), ref.cpu())
     e_rht = orc.rel_frobenius(rht.cpu(), ref.cpu())
-    assert e_rht < 0.2, f"transformed product error {e_rht}"
-    assert e_rht < e_plain, f"transform did not help on outlier data: {e_rht} vs {e_plain}"
+    assert e_rht < 0.2 and e_plain < 0.2, f"product error: transformed {e_rht}, plain {e_plain}"
     # the GEMM itself is exact on the codes: compare with the dequantized operands
     wa = orc.nvfp4_quantize_scaled(a.cpu(), 1.0, rht_signs=SIGNS)
     wb = orc.nvfp4_quantize_scaled(b.cpu(), 1.0, rht_signs=SIGNS)
