@@ -43,6 +43,11 @@
 //            rest of tensor memory), which the epilogue pulls into registers first and then
 //            releases the MMA warp.
 //
+// Options of the same kernel: alpha on the accumulator (per-tensor operand scales), a
+// block-quantizing epilogue (the output leaves as the next GEMM's row-wise operand), and a split
+// of the K loop over otherwise idle clusters with fp32 partials in a workspace that a small
+// kernel sums (outputs of a few tiles over a long K).
+//
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records a code in the
 // caller's status word, stops issuing work, lets copies in flight land and releases its
 // tensor memory before returning.
