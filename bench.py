@@ -369,6 +369,34 @@ def multi_gpu_check(ops, dev, rank, world):
     except Exception as e:   # noqa: BLE001
         res["switch_allreduce_vs_nccl_sum"] = {"ok": False, "error": f"{type(e).__name__}: {e}"[:200]}
     try:
+        from dp import CopyEngineAllReducer
+        numel = (1 << 20) + 40                      # not a multiple of world * 8: the padded tail is exercised
+        red = CopyEngineAllReducer(numel, dev)
+        gen = torch.Generator(device=dev).manual_seed(8765 + rank)
+        ok = True
+        for _ in range(3):                          # replays of the captured sequence
+            src = torch.randn(numel, device=dev, generator=gen).to(torch.bfloat16)
+            red.flat[:numel].copy_(src)
+            want = src.float()
+            dist.all_reduce(want)
+            torch.cuda.synchronize()
+            red.all_reduce()
+            torch.cuda.synchronize()
+            ops.check_status(dev)
+            got = red.flat[:numel].float()
+            ulp = torch.clamp(want.abs(), min=2.0 ** -126) * 2.0 ** -7
+            ok = ok and bool(((got - want).abs() <= ulp).all())
+            same = red.flat[:numel].clone()
+            dist.broadcast(same, src=0)
+            ok = ok and torch.equal(same, red.flat[:numel])
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        res["copy_engine_allreduce_vs_nccl_sum"] = {"ok": bool(flag.item()), "numel": numel, "calls": 3,
+                                                    "tolerance": "one bf16 step of the fp32 sum, identical on all ranks"}
+        del red
+    except Exception as e:   # noqa: BLE001
+        res["copy_engine_allreduce_vs_nccl_sum"] = {"ok": False, "error": f"{type(e).__name__}: {e}"[:300]}
+    try:
         from shard import ColumnShardedGemm
         gen = torch.Generator(device=dev).manual_seed(99)           # the same operands on every rank
         m, n, k = 1024, 2048 * world if 2048 * world <= 16384 else 16384, 2048
@@ -422,7 +450,22 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # all-reduce per step, on a side stream, can overlap the kernels of step i+1, as it does
     # under the backward pass of the previous layer in data-parallel training
     reducers = None
-    if world > 1 and os.environ.get("FP4T_ALLREDUCE", "nccl") == "switch":
+    # default: the library's copy-engine exchange (measured inside the step at 4 GPUs: 0.267-0.284 ms
+    # against 0.29-0.30 with NCCL and 0.254 with no exchange at all); FP4T_ALLREDUCE=nccl|switch|off
+    exchange = os.environ.get("FP4T_ALLREDUCE", "copy") if world > 1 else "none"
+    if exchange == "copy":
+        # reduce-scatter + all-gather on the copy engines (no SM taken from the step's kernels
+        # beyond a few-MB sum); NCCL if symmetric memory cannot be set up on these GPUs
+        try:
+            from dp import CopyEngineAllReducer
+            reducers = [CopyEngineAllReducer(OC * IC + OC, dev, reduce_ctas=int(os.environ.get("FP4T_ALLREDUCE_CTAS", "0")),
+                                             reduce=os.environ.get("FP4T_ALLREDUCE_REDUCE", "auto"))
+                        for _ in range(2)]
+        except Exception as e:   # noqa: BLE001
+            if rank == 0:
+                print(f"bench: copy-engine all-reduce unavailable ({e!r}); using NCCL", file=sys.stderr)
+            reducers, exchange = None, "nccl"
+    if exchange == "switch":
         # the library's own in-switch all-reduce (opt-in: inside the step it measured a few per
         # cent behind NCCL); NCCL if these GPUs offer no NVLink multicast
         try:
@@ -432,7 +475,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         except Exception as e:   # noqa: BLE001
             if rank == 0:
                 print(f"bench: in-switch all-reduce unavailable ({e!r}); using NCCL", file=sys.stderr)
-            reducers = None
+            reducers, exchange = None, "nccl"
     if reducers is not None:
         grad_bufs = [r.flat for r in reducers]
     else:
@@ -448,16 +491,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             torch.cuda.current_stream().wait_event(comm_done[slot])   # buffer free again
         flat = grad_bufs[slot]
         dx, dw, db = ops.linear_backward("nvfp4", g, ws, IC, True, True, True, sr=ops.SR_HASH, seed=i,
-                                         out_dw=flat[:OC * IC].view(OC, IC), out_db=flat[OC * IC:])
+                                         out_dw=flat[:OC * IC].view(OC, IC), out_db=flat[OC * IC:OC * IC + OC])
         if world > 1:
             ready = ev()
             ready.record()
             with torch.cuda.stream(comm_stream):
                 comm_stream.wait_event(ready)
-                if reducers is not None:
+                if exchange == "switch":
                     reducers[slot].all_reduce(ops.status_word(dev))
                     ops.LAUNCHES["allreduce"] += 1
-                else:
+                elif exchange == "copy":
+                    reducers[slot].all_reduce()
+                    ops.LAUNCHES["allreduce"] += 3      # two rendezvous launches and the shard sum
+                elif exchange == "nccl":
                     dist.all_reduce(flat)
                 comm_done[slot] = ev()
                 comm_done[slot].record()
@@ -580,9 +626,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate, bf16 out)", "data": "synthetic",
         "config": config,
-        "details": {"allreduce": ("none" if world == 1 else
-                                  "fp4t in-switch multimem kernel on a side stream, one call per step" if reducers is not None
-                                  else "NCCL on a side stream, one call per step"),
+        "details": {"allreduce": {"none": "none",
+                                  "off": "EXPERIMENT: no exchange (not a data-parallel step)",
+                                  "switch": "fp4t in-switch multimem kernel on a side stream, one call per step",
+                                  "copy": "fp4t reduce-scatter + all-gather on the copy engines (peer copies, one-warp "
+                                          "rendezvous, shard sum), one graph launch per step on a side stream",
+                                  "nccl": "NCCL on a side stream, one call per step"}.get(exchange, exchange),
                     "bias_grad": "fused into the dY quantizer (fp32 atomics + finishing kernel)",
                     "frac_of_nominal_fp4_peak": value / world / FP4_NOMINAL_TFLOPS},
         "sustained": {"value": world * FLOP_PER_STEP / (sus_ms_step * 1e-3) / 1e12, "unit": UNIT,

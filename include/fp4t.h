@@ -404,6 +404,35 @@ FP4T_API int fp4t_allreduce_sum_bf16_multimem(void* multicast_ptr, const void* c
                                      int64_t numel, uint32_t epoch, int ctas, int32_t* status,
                                      fp4t_stream_t stream);
 
+/*
+ * Building blocks of the same exchange with the bulk bytes on the copy engines instead of on
+ * SMs (the persistent quantizer and GEMM kernels of the next step keep every SM): a
+ * reduce-scatter + all-gather whose transfers are peer-to-peer cudaMemcpyAsync calls issued by
+ * the host side (dp.CopyEngineAllReducer), held together by these two small launches.
+ *
+ * fp4t_rank_meet: a one-warp rendezvous of the `world` ranks.  Everything that precedes the
+ *   call in stream order on each rank is complete and readable by the peers once the call has
+ *   passed on every rank.  flag_ptrs: as above (FP4T_ALLREDUCE_FLAG_WORDS words per rank, zero
+ *   before the first call; do not share the array with fp4t_allreduce_sum_bf16_multimem);
+ *   slot 0..15: independent rendezvous points; calls of one slot are counted in a device word,
+ *   so the launch may be captured in a CUDA graph and replayed.  A wait that runs out (half the
+ *   library's wait limit) writes 43 into `status`.
+ * fp4t_sum_bf16_shards: dst[i] = bf16(src[0][i] + ... + src[n_src-1][i]) accumulated in fp32 in
+ *   the order given; numel % 8 == 0, 16-byte aligned pointers, at most `ctas` CTAs.
+ */
+FP4T_API int fp4t_rank_meet(const void* const* flag_ptrs, int rank, int world, int slot, int32_t* status,
+                   fp4t_stream_t stream);
+FP4T_API int fp4t_sum_bf16_shards(void* dst, const void* const* srcs, int n_src, int64_t numel, int ctas,
+                         fp4t_stream_t stream);
+/* fp4t_reduce_shard_bf16_multimem: dst[i] = sum over the ranks of element i of the symmetric
+ *   buffer region at multicast_shard_ptr (a multicast address, 16-byte aligned; numel % 8 == 0),
+ *   added inside the switch in fp32 and rounded once to bf16; dst is local memory.  With the
+ *   rendezvous calls around it and peer copies of the reduced shards this replaces the pulls and
+ *   the sum above on GPUs that offer NVLink multicast: only 1/world of the buffer passes
+ *   through SMs. */
+FP4T_API int fp4t_reduce_shard_bf16_multimem(const void* multicast_shard_ptr, void* dst, int64_t numel, int ctas,
+                                    fp4t_stream_t stream);
+
 /* Byte-matrix transpose [rows, cols] -> [cols, rows] (E4M3 codes for the NN / NT operand
  * forms of custom/backend/csrc/cublaslt_mm_mxfp8.cu:70-88). */
 FP4T_API int fp4t_transpose_bytes(const void* src, void* dst, int64_t rows, int64_t cols,

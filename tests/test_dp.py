@@ -178,3 +178,14 @@ def test_single_process_is_a_no_op():
     r.finish()
     assert torch.equal(g, m.weight.grad)
     r.remove()
+
+
+def test_shard_plan_covers_the_buffer_in_16_byte_shards():
+    """Host arithmetic of the copy-engine exchange: every rank's shard is a whole number of
+    16-byte items and the shards cover the buffer."""
+    from dp import shard_plan
+    for world in range(1, 9):
+        for numel in (1, 7, 8, 9, 8024, 4096 * 4096 + 4096, 192 * 192 * 31 + 5):
+            shard, padded = shard_plan(numel, world)
+            assert shard % 8 == 0 and padded == shard * world and padded >= numel
+            assert padded - numel < world * 8 + world, (numel, world, shard, padded)
