@@ -33,6 +33,11 @@ _SIGNATURES = {
     "fp4t_allreduce_sum_bf16_multimem": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
                                                        ctypes.c_int, ctypes.c_int64, ctypes.c_uint32, ctypes.c_int,
                                                        ctypes.c_void_p, ctypes.c_void_p]),
+    "fp4t_layernorm_forward": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_i64, _c_i64, _c_vp, _c_vp, ctypes.c_float,
+                                               _c_vp, ctypes.c_int, _c_i64, _c_vp, _c_vp, _c_vp]),
+    "fp4t_layernorm_backward_workspace_bytes": (_c_i64, [_c_i64, _c_i64]),
+    "fp4t_layernorm_backward": (ctypes.c_int, [_c_vp, ctypes.c_int, _c_i64, _c_vp, ctypes.c_int, _c_i64, _c_vp, _c_vp, _c_vp,
+                                                _c_i64, _c_i64, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp]),
     "fp4t_rank_meet": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_void_p, ctypes.c_void_p]),
     "fp4t_reduce_shard_bf16_multimem": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,

@@ -21,7 +21,7 @@ import threading
 
 _status = {}
 _tls = threading.local()
-LAUNCHES = {"quantize": 0, "gemm": 0, "misc": 0, "allreduce": 0}   # kernels enqueued by this process
+LAUNCHES = {"quantize": 0, "gemm": 0, "misc": 0, "allreduce": 0, "norm": 0}   # kernels enqueued by this process
 
 
 def _need_cuda(*tensors):
@@ -463,3 +463,65 @@ def linear_backward(fmt, g, ws, ic, need_dx, need_dw, need_db, sr=SR_NONE, noise
         LAUNCHES["quantize"] += 2 if need_db else 1
         LAUNCHES["gemm"] += int(need_dx) + int(need_dw)
     return dx, dw, db
+
+
+# ------------------------------------------------------------------ LayerNorm
+def layernorm_forward(x, gamma, beta, eps, out_dtype):
+    """x [rows, cols] (fp32 or bf16, unit column stride) -> (y [rows, cols] in out_dtype, mean, rstd);
+    statistics in fp32.  gamma / beta: fp32 [cols]."""
+    _need_cuda(x, gamma, beta)
+    if x.ndim != 2:
+        raise ValueError("layernorm_forward takes a 2-D tensor")
+    if x.dtype not in (torch.float32, torch.bfloat16) or out_dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("layernorm runs on float32 / bfloat16 tensors")
+    rows, cols = x.shape
+    if cols % 4 or cols > 1024:
+        raise ValueError("layernorm needs a normalized width that is a multiple of 4, at most 1024")
+    if x.stride(1) != 1 or x.stride(0) % 4 or x.data_ptr() % 16:
+        x = x.contiguous()
+    dev = x.device
+    gamma = gamma.detach().to(torch.float32).contiguous()
+    beta = beta.detach().to(torch.float32).contiguous()
+    with _on_device(dev):
+        y = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+        mean = torch.empty(rows, dtype=torch.float32, device=dev)
+        rstd = torch.empty(rows, dtype=torch.float32, device=dev)
+        rc = _lib.lib().fp4t_layernorm_forward(_lib.ptr(x), _lib.dtype_code(x.dtype), rows, cols, x.stride(0),
+                                               _lib.ptr(gamma), _lib.ptr(beta), float(eps), _lib.ptr(y),
+                                               _lib.dtype_code(out_dtype), cols, _lib.ptr(mean), _lib.ptr(rstd),
+                                               _lib.stream_ptr(dev))
+        _lib.check(rc, "fp4t_layernorm_forward")
+        LAUNCHES["norm"] += 1
+    return y, mean, rstd
+
+
+def layernorm_backward(dy, x, mean, rstd, gamma):
+    """-> (dx like x, dgamma fp32 [cols], dbeta fp32 [cols]) for the forward above."""
+    _need_cuda(dy, x, mean, rstd, gamma)
+    rows, cols = x.shape
+    if dy.shape != x.shape:
+        raise ValueError("dy must have the shape of x")
+    if dy.dtype not in (torch.float32, torch.bfloat16):
+        dy = dy.to(torch.float32)
+    if dy.stride(1) != 1 or dy.stride(0) % 4 or dy.data_ptr() % 16:
+        dy = dy.contiguous()
+    if x.stride(1) != 1 or x.stride(0) % 4 or x.data_ptr() % 16:
+        x = x.contiguous()
+    dev = x.device
+    gamma = gamma.detach().to(torch.float32).contiguous()
+    with _on_device(dev):
+        L = _lib.lib()
+        dx = torch.empty((rows, cols), dtype=x.dtype, device=dev)
+        dgamma = torch.empty(cols, dtype=torch.float32, device=dev)
+        dbeta = torch.empty(cols, dtype=torch.float32, device=dev)
+        ws_bytes = L.fp4t_layernorm_backward_workspace_bytes(rows, cols)
+        if ws_bytes < 0:
+            raise RuntimeError("fp4t_layernorm_backward_workspace_bytes: unsupported shape or device")
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        rc = L.fp4t_layernorm_backward(_lib.ptr(dy), _lib.dtype_code(dy.dtype), dy.stride(0), _lib.ptr(x),
+                                       _lib.dtype_code(x.dtype), x.stride(0), _lib.ptr(mean), _lib.ptr(rstd),
+                                       _lib.ptr(gamma), rows, cols, _lib.ptr(dx), cols, _lib.ptr(dgamma), _lib.ptr(dbeta),
+                                       _lib.ptr(ws), _lib.stream_ptr(dev))
+        _lib.check(rc, "fp4t_layernorm_backward")
+        LAUNCHES["norm"] += 2
+    return dx, dgamma, dbeta

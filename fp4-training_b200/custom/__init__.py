@@ -9,6 +9,7 @@ from .linear.nvf4fwd_mxf8bwd import CublasltFwdNvfp4BwdMxfp8Linear
 
 from .linear.cuda_aten import AddmmLinear
 from .linear.fake_mxfp8 import FakeMxfp8Linear
+from .norm import FusedLayerNorm
 
 __all__ = [
     "CustomLinear",
@@ -18,4 +19,5 @@ __all__ = [
     "CublasltFwdNvfp4BwdMxfp8Linear",
     "FakeMxfp8Linear",
     "AddmmLinear",
+    "FusedLayerNorm",
 ]

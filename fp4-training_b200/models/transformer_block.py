@@ -10,6 +10,7 @@ from custom import (
     CublasltMxfp8Linear,
     CublasltNvfp4Linear,
     CustomLinear,
+    FusedLayerNorm,
 )
 
 LINEAR_IMPL = {
@@ -31,12 +32,12 @@ class AttentionBlock(nn.Module):
     (models/transformer_block.py:74,95) attn_scale is 1 / dh**-0.5, i.e. the scores are
     MULTIPLIED by sqrt(dh); loss-curve parity depends on keeping that."""
 
-    def __init__(self, E, H, dropout=0.1, impl="torch"):
+    def __init__(self, E, H, dropout=0.1, impl="torch", fused_norm=False):
         super().__init__()
         assert E % H == 0, "head size is not multiple of embedding size"
         self.E, self.H, self.dh = E, H, E // H
         self.attn_scale = 1 / (self.dh ** -0.5)
-        self.preln = nn.LayerNorm(E)
+        self.preln = FusedLayerNorm(E) if fused_norm else nn.LayerNorm(E)
         linear = LINEAR_IMPL[impl]
         self.q_proj = linear(E, E)
         self.k_proj = linear(E, E)
@@ -57,14 +58,16 @@ class AttentionBlock(nn.Module):
 
 
 class TransformerBlock(nn.Module):
-    def __init__(self, E, F, H, dropout=0.1, impl="torch", fuse_gelu=False):
+    def __init__(self, E, F, H, dropout=0.1, impl="torch", fuse_gelu=False, fused_norm=False):
         super().__init__()
         self.E, self.F, self.H, self.impl = E, F, H, impl
         self.fuse_gelu = fuse_gelu      # an addition: see forward()
-        self.attn = AttentionBlock(E, H, dropout, impl=impl)
+        # fused_norm (an addition): the two `preln` modules run on the library's LayerNorm kernels
+        # (same parameters and state dict as nn.LayerNorm)
+        self.attn = AttentionBlock(E, H, dropout, impl=impl, fused_norm=fused_norm)
         linear = LINEAR_IMPL[impl]
         self.ffn = nn.ModuleDict({
-            "preln": nn.LayerNorm(E),
+            "preln": FusedLayerNorm(E) if fused_norm else nn.LayerNorm(E),
             "up_proj": linear(E, F),
             "act": nn.GELU(),
             "act_dropout": nn.Dropout(dropout),

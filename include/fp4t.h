@@ -433,6 +433,28 @@ FP4T_API int fp4t_sum_bf16_shards(void* dst, const void* const* srcs, int n_src,
 FP4T_API int fp4t_reduce_shard_bf16_multimem(const void* multicast_shard_ptr, void* dst, int64_t numel, int ctas,
                                     fp4t_stream_t stream);
 
+/*
+ * LayerNorm in front of the quantized projections (replaces nn.LayerNorm `preln` in the
+ * reference's blocks, models/transformer_block.py:45-52,89-93, together with the cast of its
+ * output to the projections' input dtype that autocast inserts).
+ *
+ * forward:  y[r, :] = (x[r, :] - mean_r) * rstd_r * gamma + beta, statistics in fp32 over the
+ *   `cols` elements of a row (biased variance, rstd = 1 / sqrt(var + eps)), x and y each fp32 or
+ *   bf16 (FP4T_DT_*), row pitches ldx / ldy in elements; mean and rstd ([rows] fp32) are kept
+ *   for the backward pass.  cols % 4 == 0, cols <= 1024, 16-byte aligned rows.
+ * backward: dx (dtype and pitch rule of x) and dgamma / dbeta ([cols] fp32) from dy (fp32 or
+ *   bf16), x and the saved statistics.  workspace: fp4t_layernorm_backward_workspace_bytes(rows,
+ *   cols) bytes, 16-byte aligned; the column sums are added in a fixed order (reproducible).
+ */
+FP4T_API int fp4t_layernorm_forward(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ldx,
+                           const float* gamma, const float* beta, float eps, void* y, int y_dtype,
+                           int64_t ldy, float* mean, float* rstd, fp4t_stream_t stream);
+FP4T_API int64_t fp4t_layernorm_backward_workspace_bytes(int64_t rows, int64_t cols);
+FP4T_API int fp4t_layernorm_backward(const void* dy, int dy_dtype, int64_t lddy, const void* x, int x_dtype,
+                            int64_t ldx, const float* mean, const float* rstd, const float* gamma,
+                            int64_t rows, int64_t cols, void* dx, int64_t lddx, float* dgamma,
+                            float* dbeta, void* workspace, fp4t_stream_t stream);
+
 /* Byte-matrix transpose [rows, cols] -> [cols, rows] (E4M3 codes for the NN / NT operand
  * forms of custom/backend/csrc/cublaslt_mm_mxfp8.cu:70-88). */
 FP4T_API int fp4t_transpose_bytes(const void* src, void* dst, int64_t rows, int64_t cols,
