@@ -991,21 +991,30 @@ def run_tinyvit(args, rank, world, local_rank):
         sampler.start()
     l0 = sum(ops.LAUNCHES.values())
     m0 = sampler.mark()
-    res = train("cublaslt_nvfp4", steps=steps, warmup=warm, batch=512, depth=6, seed=0, graph=True)
+    # headline: the model with the library's block-level options (LayerNorm kernels, q / k / v as one
+    # quantization + one GEMM); the same recipe on the reference's module tree, and plain bf16
+    # torch with and without the LayerNorm kernels, are measured beside it
+    res = train("cublaslt_nvfp4", steps=steps, warmup=warm, batch=512, depth=6, seed=0, graph=True,
+                fused_norm=True, fuse_qkv=True)
     m1 = sampler.mark()
     launches_captured = sum(ops.LAUNCHES.values()) - l0
-    eager = train("cublaslt_nvfp4", steps=min(steps, 50), warmup=warm, batch=512, depth=6, seed=0)
+    plain = train("cublaslt_nvfp4", steps=steps, warmup=warm, batch=512, depth=6, seed=0, graph=True)
+    eager = train("cublaslt_nvfp4", steps=min(steps, 50), warmup=warm, batch=512, depth=6, seed=0,
+                  fused_norm=True, fuse_qkv=True)
     base = train("torch", steps=min(steps, 50), warmup=warm, batch=512, depth=6, seed=0)
     base_graph = train("torch", steps=steps, warmup=warm, batch=512, depth=6, seed=0, graph=True)
+    base_norm_graph = train("torch", steps=steps, warmup=warm, batch=512, depth=6, seed=0, graph=True, fused_norm=True)
     sampler.stop()
     ops.check_status(dev)
     if rank != 0:
         return
-    per_step = 36 * 8      # per projection: 3 launches forward (W, X, GEMM), 5 backward (zero, dY, finish, dgrad, wgrad)
+    # per block: q/k/v stacked + o + up + down = 4 projection groups of 3 launches forward (W, X, GEMM) and
+    # 5-6 backward (zero, dY, finish, dgrad, wgrad + split-K sum), 2 LayerNorms of 1 + 2 launches
+    per_step = 6 * (4 * 8 + 2 * 3)
     line = {"metric": "tinyvit_nvfp4_steps_per_s", "value": res["steps_per_s"], "unit": "steps/s", "n_gpus": world,
             "steps": steps, "warmup": warm, "ms_per_step": 1e3 / res["steps_per_s"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "nvfp4 linears (36 projections), bf16 autocast elsewhere", "data": "synthetic",
+            "dtype": "nvfp4 linears (36 projections; q/k/v stacked), bf16 autocast elsewhere", "data": "synthetic",
             "config": {"workload": "TinyViT-style classifier: 28x28x1, patch 4, hidden 192, depth 6, 3 heads, MLP 768, "
                                    "batch 512 per GPU, AdamW lr 1e-3, seed 0",
                        "l2": "model and activations fit L2; each step draws a fresh batch on the device",
@@ -1014,10 +1023,15 @@ def run_tinyvit(args, rank, world, local_rank):
                                     "one all-reduce of the flat gradient buffer between them"},
             "images_per_s": res["images_per_s"], "first_loss": res["first_loss"], "last_loss": res["last_loss"],
             "loss_curve": [round(v, 4) for v in res["losses"][:: max(1, len(res["losses"]) // 25)]],
+            "model_options": {"fused_norm": True, "fuse_qkv": True},
             "eager_steps_per_s": eager["steps_per_s"],
+            "nvfp4_reference_module_tree_graph_steps_per_s": plain["steps_per_s"],
             "bf16_torch_steps_per_s": base["steps_per_s"], "bf16_torch_graph_steps_per_s": base_graph["steps_per_s"],
+            "bf16_torch_graph_with_fused_norm_steps_per_s": base_norm_graph["steps_per_s"],
             "speedup_over_bf16_torch": res["steps_per_s"] / base["steps_per_s"],
             "speedup_over_bf16_torch_graph": res["steps_per_s"] / base_graph["steps_per_s"],
+            "speedup_over_bf16_torch_graph_with_fused_norm": res["steps_per_s"] / base_norm_graph["steps_per_s"],
+            "speedup_reference_module_tree_over_bf16_torch_graph": plain["steps_per_s"] / base_graph["steps_per_s"],
             "gpu_launches": per_step * steps, "gpu_launches_note":
                 f"{per_step} kernels of this library per replayed step ({launches_captured} enqueued by the host for warm-up and capture)",
             "clocks": sampler.summary(m0, m1)}

@@ -207,31 +207,59 @@ __global__ void __launch_bounds__(kNormThreads) layernorm_bwd_kernel(const NormB
   }
 }
 
-// dgamma[c] / dbeta[c] = sum over the CTAs' partial rows, in CTA order
-__global__ void layernorm_param_grad_kernel(const float* __restrict__ partial, int nparts, int cols,
-                                            float* __restrict__ dgamma, float* __restrict__ dbeta) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= 2 * cols) return;
+// dgamma[c] / dbeta[c] = sum over the CTAs' partial rows.  One CTA per 32 columns of the
+// [2 cols] row; warp w adds rows w, w + 32, ... (four independent chains), then the 32 warps'
+// sums are added in warp order: a fixed association, whatever the scheduling.
+constexpr int kParamWarps = 32;
+__global__ void __launch_bounds__(32 * kParamWarps) layernorm_param_grad_kernel(const float* __restrict__ partial, int nparts,
+                                                                                int cols, float* __restrict__ dgamma,
+                                                                                float* __restrict__ dbeta) {
+  __shared__ float red[kParamWarps][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + lane;
+  const size_t pitch = (size_t)2 * cols;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int k = 0;
-  for (; k + 4 <= nparts; k += 4) {
-    s0 += partial[(size_t)(k + 0) * 2 * cols + i];
-    s1 += partial[(size_t)(k + 1) * 2 * cols + i];
-    s2 += partial[(size_t)(k + 2) * 2 * cols + i];
-    s3 += partial[(size_t)(k + 3) * 2 * cols + i];
+  if (i < 2 * cols) {
+    int k = warp;
+    for (; k + 3 * kParamWarps < nparts; k += 4 * kParamWarps) {
+      s0 += partial[(size_t)k * pitch + i];
+      s1 += partial[(size_t)(k + kParamWarps) * pitch + i];
+      s2 += partial[(size_t)(k + 2 * kParamWarps) * pitch + i];
+      s3 += partial[(size_t)(k + 3 * kParamWarps) * pitch + i];
+    }
+    for (; k < nparts; k += kParamWarps) s0 += partial[(size_t)k * pitch + i];
   }
-  for (; k < nparts; ++k) s0 += partial[(size_t)k * 2 * cols + i];
-  const float s = (s0 + s1) + (s2 + s3);
-  if (i < cols) dgamma[i] = s;
-  else dbeta[i - cols] = s;
+  red[warp][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (warp == 0 && i < 2 * cols) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kParamWarps; ++w) s += red[w][lane];
+    if (i < cols) dgamma[i] = s;
+    else dbeta[i - cols] = s;
+  }
 }
 
-int norm_grid(int64_t rows) {
+// One wave of CTAs: as many as are resident at once (all warps walk the rows with the same
+// stride, so a second, partial wave would run at a fraction of the machine), at most 4 per SM
+// to keep the number of partial parameter-gradient rows small.
+template <typename Kernel>
+int norm_grid(Kernel kern, int64_t rows) {
   const int sms = sm_count();
   if (sms <= 0) return -1;
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kNormThreads, 0) != cudaSuccess || occ <= 0) {
+    cudaGetLastError();
+    occ = 1;
+  }
+  if (occ > 4) occ = 4;
   const int64_t want = ceil_div(rows, kNormWarps);
-  const int64_t cap = (int64_t)sms * 4;           // enough rows in flight per SM, few enough partial rows
+  const int64_t cap = (int64_t)sms * occ;
   return (int)(want < cap ? want : cap);
+}
+int max_norm_grid() {
+  const int sms = sm_count();
+  return sms > 0 ? sms * 4 : -1;
 }
 
 int check_common(const char* name, int64_t rows, int64_t cols) {
@@ -260,7 +288,8 @@ extern "C" int fp4t_layernorm_forward(const void* x, int x_dtype, int64_t rows, 
   FP4T_REQUIRE(aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta), "%s: pointers must be 16-byte aligned", name);
   FP4T_REQUIRE(eps >= 0.0f, "%s: eps must not be negative", name);
   if (rows == 0) return FP4T_OK;
-  const int grid = norm_grid(rows);
+  const int grid = cols <= 256 ? norm_grid(layernorm_fwd_kernel<2>, rows)
+                   : cols <= 512 ? norm_grid(layernorm_fwd_kernel<4>, rows) : norm_grid(layernorm_fwd_kernel<8>, rows);
   if (grid <= 0) {
     set_error("%s: the current device is not an sm_100 part", name);
     return FP4T_ERR_DEVICE;
@@ -276,7 +305,7 @@ extern "C" int fp4t_layernorm_forward(const void* x, int x_dtype, int64_t rows, 
 
 extern "C" int64_t fp4t_layernorm_backward_workspace_bytes(int64_t rows, int64_t cols) {
   if (rows < 0 || cols <= 0 || cols > kNormMaxCols) return -1;
-  const int grid = norm_grid(rows > 0 ? rows : 1);
+  const int grid = max_norm_grid();     // an upper bound of the backward kernel's grid
   if (grid <= 0) return -1;
   return (int64_t)grid * 2 * cols * (int64_t)sizeof(float);
 }
@@ -301,7 +330,8 @@ extern "C" int fp4t_layernorm_backward(const void* dy, int dy_dtype, int64_t ldd
     FP4T_CUDA(cudaMemsetAsync(dbeta, 0, (size_t)cols * sizeof(float), s));
     return FP4T_OK;
   }
-  const int grid = norm_grid(rows);
+  const int grid = cols <= 256 ? norm_grid(layernorm_bwd_kernel<2>, rows)
+                   : cols <= 512 ? norm_grid(layernorm_bwd_kernel<4>, rows) : norm_grid(layernorm_bwd_kernel<8>, rows);
   if (grid <= 0) {
     set_error("%s: the current device is not an sm_100 part", name);
     return FP4T_ERR_DEVICE;
@@ -311,8 +341,7 @@ extern "C" int fp4t_layernorm_backward(const void* dy, int dy_dtype, int64_t ldd
   else if (cols <= 512) layernorm_bwd_kernel<4><<<grid, kNormThreads, 0, s>>>(p);
   else layernorm_bwd_kernel<8><<<grid, kNormThreads, 0, s>>>(p);
   FP4T_CUDA(cudaGetLastError());
-  const int threads = 128;
-  layernorm_param_grad_kernel<<<(unsigned)ceil_div(2 * cols, threads), threads, 0, s>>>(
+  layernorm_param_grad_kernel<<<(unsigned)ceil_div(2 * cols, 32), 32 * kParamWarps, 0, s>>>(
       static_cast<const float*>(workspace), grid, (int)cols, dgamma, dbeta);
   FP4T_CUDA(cudaGetLastError());
   return FP4T_OK;

@@ -138,3 +138,13 @@ class CublasltMxfp8Linear(CustomLinear):
         if not F.is_stock(self.quantizers, STOCK):
             return self.forward(torch.nn.functional.gelu(pre_activation))
         return F.gelu_linear(self, pre_activation, "mxfp8", False)
+
+    @staticmethod
+    def forward_stacked(modules, input):
+        """[m(input) for m in modules] for layers of this class that share their input (q / k / v):
+        one quantization of the input and one GEMM over the stacked weights.  Falls back to the
+        separate calls where a layer's quantizer table is customised."""
+        ok = all(F.is_stock(m.quantizers, STOCK) for m in modules)
+        if not ok or input.shape[-1] % 32 or sum(m.out_features for m in modules) % 32:
+            return [m(input) for m in modules]
+        return F.stacked_linear(modules, input, "mxfp8", False)

@@ -150,3 +150,15 @@ class CublasltNvfp4Linear(CustomLinear):
         if not F.is_stock(self.quantizers, STOCK):
             return self.forward(torch.nn.functional.gelu(pre_activation))
         return F.gelu_linear(self, pre_activation, "nvfp4", True)
+
+    @staticmethod
+    def forward_stacked(modules, input):
+        """[m(input) for m in modules] for layers of this class that share their input (q / k / v):
+        one quantization of the input and one GEMM over the stacked weights.  Falls back to the
+        separate calls where a layer's quantizer table is customised, a gradient tensor scale is
+        set, or the bit-exact stochastic-rounding mode is on (its draws follow the separate
+        layers' order)."""
+        ok = all(F.is_stock(m.quantizers, STOCK) and m.grad_tensor_scale == 1.0 for m in modules) and not F.parity_mode()
+        if not ok or input.shape[-1] % 32 or sum(m.out_features for m in modules) % 32:
+            return [m(input) for m in modules]
+        return F.stacked_linear(modules, input, "nvfp4", True)

@@ -32,8 +32,9 @@ class AttentionBlock(nn.Module):
     (models/transformer_block.py:74,95) attn_scale is 1 / dh**-0.5, i.e. the scores are
     MULTIPLIED by sqrt(dh); loss-curve parity depends on keeping that."""
 
-    def __init__(self, E, H, dropout=0.1, impl="torch", fused_norm=False):
+    def __init__(self, E, H, dropout=0.1, impl="torch", fused_norm=False, fuse_qkv=False):
         super().__init__()
+        self.fuse_qkv = fuse_qkv        # an addition: q / k / v as one quantization + one GEMM over stacked weights
         assert E % H == 0, "head size is not multiple of embedding size"
         self.E, self.H, self.dh = E, H, E // H
         self.attn_scale = 1 / (self.dh ** -0.5)
@@ -49,22 +50,26 @@ class AttentionBlock(nn.Module):
         B, L, E = x.shape
         residual = x
         x = self.preln(x)
-        q = self.q_proj(x).view(B, L, self.H, self.dh).transpose(1, 2)
-        k_t = self.k_proj(x).view(B, L, self.H, self.dh).transpose(1, 2).transpose(-2, -1)
-        v = self.v_proj(x).view(B, L, self.H, self.dh).transpose(1, 2)
+        if self.fuse_qkv and hasattr(self.q_proj, "forward_stacked"):
+            q, k, v = self.q_proj.forward_stacked([self.q_proj, self.k_proj, self.v_proj], x)
+        else:
+            q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        q = q.view(B, L, self.H, self.dh).transpose(1, 2)
+        k_t = k.view(B, L, self.H, self.dh).transpose(1, 2).transpose(-2, -1)
+        v = v.view(B, L, self.H, self.dh).transpose(1, 2)
         prob = self.dropout(F.softmax((q @ k_t) * self.attn_scale, dim=-1))
         attn = (prob @ v).transpose(1, 2).contiguous().view(B, L, E)
         return residual + self.o_proj(attn)
 
 
 class TransformerBlock(nn.Module):
-    def __init__(self, E, F, H, dropout=0.1, impl="torch", fuse_gelu=False, fused_norm=False):
+    def __init__(self, E, F, H, dropout=0.1, impl="torch", fuse_gelu=False, fused_norm=False, fuse_qkv=False):
         super().__init__()
         self.E, self.F, self.H, self.impl = E, F, H, impl
         self.fuse_gelu = fuse_gelu      # an addition: see forward()
         # fused_norm (an addition): the two `preln` modules run on the library's LayerNorm kernels
         # (same parameters and state dict as nn.LayerNorm)
-        self.attn = AttentionBlock(E, H, dropout, impl=impl, fused_norm=fused_norm)
+        self.attn = AttentionBlock(E, H, dropout, impl=impl, fused_norm=fused_norm, fuse_qkv=fuse_qkv)
         linear = LINEAR_IMPL[impl]
         self.ffn = nn.ModuleDict({
             "preln": FusedLayerNorm(E) if fused_norm else nn.LayerNorm(E),
