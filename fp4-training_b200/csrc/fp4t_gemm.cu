@@ -7,7 +7,7 @@
 // in the 128x4 tile layout, which is exactly the 32-lane x 16-byte image that one
 // `tcgen05.cp ... 32x128b.warpx4` drops into tensor memory for the MMA to consume.
 //
-// One persistent kernel, 256 threads, in two forms selected at compile time:
+// One persistent kernel, 256 or 384 threads, in two forms selected at compile time:
 //   kCtas == 2  a cluster of two CTAs (two SMs) works on one 256 x kBN tile with cta_group::2
 //               MMAs.  Each CTA holds its own 128 rows of P and HALF of the Q rows in shared
 //               memory (the MMA reads both halves across the pair), so the Q traffic per SM is
@@ -35,7 +35,8 @@
 //   warp 2   tensor-memory allocation, then the tile scheduler (leader): tile indices from the
 //            stream's device counter (or the static order), published to both CTAs through a
 //            small queue in shared memory.
-//   warps 4-7 epilogue: tcgen05.ld 32 lanes x 32 columns at a time, + bias, convert, swizzled
+//   warps 4-7 (4-11 for short K loops: two per lane quadrant, half of the tile's columns each)
+//            epilogue: tcgen05.ld 32 lanes x 32 columns at a time, + bias, convert, swizzled
 //            staging tiles in shared memory, one tiled TMA store per chunk (clipped at the
 //            matrix edges; per-thread stores when base or pitch are not 16-byte aligned).  Two
 //            accumulators alternate so the epilogue of tile i overlaps the main loop of tile
@@ -64,7 +65,13 @@ enum { kNvfp4 = 0, kMxfp8 = 1 };
 
 constexpr int kBM = 128;             // rows of P per CTA tile (the MMA M per CTA)
 constexpr int kTmemCols = 512;
-constexpr int kGemmThreads = 256;
+// Epilogue warps per CTA (a template parameter of the kernel): 4, one per tensor-memory lane
+// quadrant, or 8, two per quadrant with half of a tile's columns each.  A tile with a long K loop
+// hides the four-warp epilogue under the next tile's MMAs and runs 2-3 % faster without the extra
+// warps resident (measured at K = 4096); a tile whose MMAs take less time than draining it (K up
+// to kWideEpilogueStages stages) is bound by the epilogue and gets eight.
+constexpr int kWideEpilogueStages = 8;
+constexpr int gemm_threads(int epi_warps) { return 128 + 32 * epi_warps; }   // producer, MMA issuer, scheduler, an idle warp, epilogue
 constexpr int kSched = 4;            // depth of the in-kernel tile queue
 
 struct GemmParams {
@@ -430,7 +437,7 @@ __device__ __forceinline__ void quant_chunk(const GemmParams& g, const int row, 
 // ------------------------------------------------------------------------------------
 // The kernel
 // ------------------------------------------------------------------------------------
-template <int kFmt, int kBN, int kCtas>
+template <int kFmt, int kBN, int kCtas, int kEpiWarps = 4>
 struct Cfg {
   static constexpr int kSfChunks = kFmt == kNvfp4 ? 4 : 1;   // 512-byte scale tiles per 128 rows per stage
   static constexpr int kOuterB = (kBN + 127) / 128;          // 128-row scale tiles of Q per tile (a 64-column tile uses half of one)
@@ -443,7 +450,7 @@ struct Cfg {
   static constexpr int kStageBytes = (kLoadBytes + 1023) / 1024 * 1024;          // operand tiles start 1024-byte aligned
   static constexpr int kSfaOff = kABytes + kBBytes;
   static constexpr int kSfbOff = kSfaOff + kSfaBytes;
-  static constexpr int kEpiBytes = 4 * 4096;                 // staging tiles of the four epilogue warps
+  static constexpr int kEpiBytes = kEpiWarps * 4096;         // staging tiles of the epilogue warps
   static constexpr int kBarBytes = 512;
   // the dynamic shared memory window is declared 1024-byte aligned (checked at run time), so no slack
   static constexpr int kBudget = 227 * 1024 - kBarBytes - kEpiBytes;
@@ -464,7 +471,7 @@ struct Cfg {
   static constexpr int kEarlyChunks = (2 * kBN <= kSfBuf0) ? 0 : (2 * kBN - kSfBuf0 + 31) / 32;
   static constexpr int kAccStride = kBN - 32 * kEarlyChunks;
   static constexpr int kSfBoxElems = kSfChunks * 64;         // 8-byte elements per scale box row
-  static constexpr int kSchedReaders = kCtas == 2 ? 11 : 6;  // roles that read each queue entry: producer, epilogue x4 (+ the MMA issuer in the leader)
+  static constexpr int kSchedReaders = kCtas * (1 + kEpiWarps) + 1;  // roles that read each queue entry: per CTA the producer and the epilogue warps, + the MMA issuer in the leader
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   static_assert(kStages >= 3, "too few stages");
   static_assert(kAccStride + kBN <= kSfBuf0, "tensor memory budget");
@@ -472,12 +479,12 @@ struct Cfg {
   static_assert((2 * kStages + 2 + 2 * kSched) * 8 + 8 + 4 * kSched <= kBarBytes, "barrier block");
 };
 
-template <int kFmt, int kBN, int kCtas>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int kFmt, int kBN, int kCtas, int kEpiWarps>
+__global__ void __launch_bounds__(gemm_threads(kEpiWarps), 1)
 gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                         const __grid_constant__ CUtensorMap map_psf, const __grid_constant__ CUtensorMap map_qsf,
                         const __grid_constant__ CUtensorMap map_d, const GemmParams g) {
-  using C = Cfg<kFmt, kBN, kCtas>;
+  using C = Cfg<kFmt, kBN, kCtas, kEpiWarps>;
   constexpr bool kPair = kCtas == 2;
   extern __shared__ __align__(1024) uint8_t smem_dyn[];
   uint8_t* smem_gen = smem_dyn;
@@ -513,7 +520,7 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       mbar_init(bar_empty + 8 * s, 1);     // one tcgen05.commit
     }
     mbar_init(bar_tmem_full, 1);
-    mbar_init(bar_tmem_empty, 4 * kCtas);  // four epilogue warps in each CTA
+    mbar_init(bar_tmem_empty, kEpiWarps * kCtas);  // every epilogue warp of every CTA
     for (int q = 0; q < kSched; ++q) {
       mbar_init(bar_sched_full + 8 * q, 1);
       mbar_init(bar_sched_empty + 8 * q, C::kSchedReaders);
@@ -724,8 +731,15 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
    __syncwarp();
   } else if (warp >= 4) {
     // ------------------------------ epilogue (every CTA) ------------------------------
+    // A warp reads the 32 tensor-memory lanes of its quadrant (warp & 3); with eight warps the two
+    // of a quadrant take half of the tile's 32-column chunks each.
     const int quad = warp & 3;
-    uint8_t* epi_buf = smem_gen + C::kEpi0 + quad * 4096;
+    constexpr int kParts = kEpiWarps / 4;
+    const int half = (warp - 4) >> 2;
+    constexpr int kHalf = C::kChunks / kParts;
+    static_assert(kEpiWarps == 4 || kEpiWarps == 8, "one or two epilogue warps per lane quadrant");
+    static_assert(C::kChunks % kParts == 0 && C::kEarlyChunks <= kHalf, "chunks split evenly over the warps of a quadrant");
+    uint8_t* epi_buf = smem_gen + C::kEpi0 + (warp - 4) * 4096;
     uint32_t n_emit = 0;
     int it = 0;
     for (;; ++it) {
@@ -760,31 +774,48 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
       };
       if (C::kEarlyChunks > 0) {
         // The columns the other accumulator overlaps (the last ones of accumulator 0, the first
-        // ones of accumulator 1) go to registers first.
+        // ones of accumulator 1) go to registers first, in the warps whose part holds them.  With
+        // two warps per quadrant the other one signals at once: it is done with the previous tile,
+        // which is all the MMA warp needs to know from it before that tile's accumulator is reused.
         constexpr int kE = C::kEarlyChunks > 0 ? C::kEarlyChunks : 1;
-        const int e0 = (it & 1) == 0 ? C::kChunks - kE : 0;
-        uint32_t early[kE][32];
+        const bool acc0 = (it & 1) == 0;
+        const bool owner = acc0 ? half == kParts - 1 : half == 0;
+        if (owner) {
+          const int e0 = acc0 ? C::kChunks - kE : 0;
+          uint32_t early[kE][32];
 #pragma unroll
-        for (int e = 0; e < kE; ++e) tc_ld32(acc + (uint32_t)((e0 + e) * 32), early[e]);
-        tc_wait_ld();
-        release();
-#pragma unroll
-        for (int e = 0; e < kE; ++e) put(col_base + (e0 + e) * 32, early[e]);
-        const int r0 = (it & 1) == 0 ? 0 : kE;
-#pragma unroll 1
-        for (int ci = 0; ci < C::kChunks - kE; ++ci) {
-          uint32_t r[32];
-          tc_ld32(acc + (uint32_t)((r0 + ci) * 32), r);
+          for (int e = 0; e < kE; ++e) tc_ld32(acc + (uint32_t)((e0 + e) * 32), early[e]);
           tc_wait_ld();
-          put(col_base + (r0 + ci) * 32, r);
+          release();
+#pragma unroll
+          for (int e = 0; e < kE; ++e) put(col_base + (e0 + e) * 32, early[e]);
+          const int r0 = acc0 ? (kParts - 1) * kHalf : kE;
+#pragma unroll 1
+          for (int ci = 0; ci < kHalf - kE; ++ci) {
+            uint32_t r[32];
+            tc_ld32(acc + (uint32_t)((r0 + ci) * 32), r);
+            tc_wait_ld();
+            put(col_base + (r0 + ci) * 32, r);
+          }
+        } else {
+          release();
+          const int r0 = half * kHalf;
+#pragma unroll 1
+          for (int ci = 0; ci < kHalf; ++ci) {
+            uint32_t r[32];
+            tc_ld32(acc + (uint32_t)((r0 + ci) * 32), r);
+            tc_wait_ld();
+            put(col_base + (r0 + ci) * 32, r);
+          }
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < C::kChunks; ++c) {
+        for (int ci = 0; ci < kHalf; ++ci) {
+          const int c = half * kHalf + ci;
           uint32_t r[32];
           tc_ld32(acc + (uint32_t)(c * 32), r);
           tc_wait_ld();
-          if (c == C::kChunks - 1) release();
+          if (ci == kHalf - 1) release();
           put(col_base + c * 32, r);
         }
       }
@@ -843,14 +874,14 @@ int make_sf_map(CUtensorMap* map, const void* base, int64_t outer, int64_t ntx, 
 }
 
 // Clusters of kCtas CTAs that can be resident at once (one CTA per SM), per device.
-template <int kFmt, int kBN, int kCtas>
+template <int kFmt, int kBN, int kCtas, int kEpiWarps = 4>
 int max_clusters() {
   static int cached[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (cached[dev] == 0) {
-    using C = Cfg<kFmt, kBN, kCtas>;
-    auto kern = gemm_blockscaled_kernel<kFmt, kBN, kCtas>;
+    using C = Cfg<kFmt, kBN, kCtas, kEpiWarps>;
+    auto kern = gemm_blockscaled_kernel<kFmt, kBN, kCtas, kEpiWarps>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       cached[dev] = -1;
@@ -862,7 +893,7 @@ int max_clusters() {
     } else {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(kCtas * 148, 1, 1);
-      cfg.blockDim = dim3(kGemmThreads, 1, 1);
+      cfg.blockDim = dim3(gemm_threads(kEpiWarps), 1, 1);
       cfg.dynamicSmemBytes = C::kSmemBytes;
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
@@ -881,10 +912,10 @@ int max_clusters() {
   return cached[dev];
 }
 
-template <int kFmt, int kBN, int kCtas>
+template <int kFmt, int kBN, int kCtas, int kEpiWarps>
 int launch_gemm(const void* p_codes, const void* q_codes, const GemmParams& g0, int64_t kbytes, int clusters,
                 cudaStream_t stream) {
-  using C = Cfg<kFmt, kBN, kCtas>;
+  using C = Cfg<kFmt, kBN, kCtas, kEpiWarps>;
   GemmParams g = g0;
   g.n_tiles = (int)ceil_div(g.cols, kBN);
   CUtensorMap map_p, map_q, map_psf, map_qsf;
@@ -908,10 +939,14 @@ int launch_gemm(const void* p_codes, const void* q_codes, const GemmParams& g0, 
   const int lim = sm_limit();
   if (lim > 0 && lim / kCtas < clusters) clusters = lim / kCtas > 0 ? lim / kCtas : 1;
   const int nclusters = cluster_tiles < clusters ? cluster_tiles : clusters;
-  auto kern = gemm_blockscaled_kernel<kFmt, kBN, kCtas>;
+  if (max_clusters<kFmt, kBN, kCtas, kEpiWarps>() <= 0) {   // also raises the kernel's shared-memory limit, once
+    set_error("gemm: the kernel cannot be resident on this device");
+    return FP4T_ERR_DEVICE;
+  }
+  auto kern = gemm_blockscaled_kernel<kFmt, kBN, kCtas, kEpiWarps>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kCtas * nclusters, 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.blockDim = dim3(gemm_threads(kEpiWarps), 1, 1);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -950,7 +985,10 @@ int launch_maybe_split(const void* p_codes, const void* q_codes, const GemmParam
     if (s * slice_bytes > sk.ws_bytes) s = sk.ws_bytes / slice_bytes;
     if (s >= 2) splits = (int)s;
   }
-  if (splits == 1) return launch_gemm<kFmt, kBN, kCtas>(p_codes, q_codes, g, kbytes, clusters, stream);
+  if (splits == 1) {
+    if (g.k_stages <= kWideEpilogueStages) return launch_gemm<kFmt, kBN, kCtas, 8>(p_codes, q_codes, g, kbytes, clusters, stream);
+    return launch_gemm<kFmt, kBN, kCtas, 4>(p_codes, q_codes, g, kbytes, clusters, stream);
+  }
   GemmParams gs = g;
   gs.ks_per_split = (int)ceil_div(g.k_stages, splits);
   gs.splits = (int)ceil_div(g.k_stages, gs.ks_per_split);     // no empty split
@@ -960,7 +998,9 @@ int launch_maybe_split(const void* p_codes, const void* q_codes, const GemmParam
   gs.out_f32 = 1;
   gs.bias = nullptr;
   gs.vec_ok = gs.tma_ok = (reinterpret_cast<uintptr_t>(sk.ws) % 16 == 0) && ((g.cols * 4) % 16 == 0);
-  int rc = launch_gemm<kFmt, kBN, kCtas>(p_codes, q_codes, gs, kbytes, clusters, stream);
+  int rc = gs.ks_per_split <= kWideEpilogueStages
+               ? launch_gemm<kFmt, kBN, kCtas, 8>(p_codes, q_codes, gs, kbytes, clusters, stream)
+               : launch_gemm<kFmt, kBN, kCtas, 4>(p_codes, q_codes, gs, kbytes, clusters, stream);
   if (rc != FP4T_OK) return rc;
   const int64_t total = (int64_t)g.rows * g.cols;
   cudaLaunchConfig_t cfg = {};
