@@ -49,12 +49,20 @@ class Nvfp4Matmul(torch.autograd.Function):
             raise ValueError("Input tensor must be 2D for nvfp4 quantization")
         X = X.contiguous()
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        # wgrad contracts over the batch and dgrad over out_features: an FP4 GEMM's K must be a
+        # multiple of 32 (rows of 16-byte multiples).  The forward pass is defined for such shapes
+        # (inference under grad mode, the reference's own forward-only checks); the backward pass is
+        # not, and says so as soon as it is entered, naming the dimension.
+        ctx.shape_error = None
         if need_dw and X.shape[0] % 32:
-            # wgrad contracts over the batch: its K must be a multiple of 32 (FP4 rows of 16-byte
-            # multiples).  Said here, not in the middle of the backward pass.
-            raise ValueError(f"nvfp4 weight gradients need the flattened batch ({X.shape[0]}) to be a multiple of 32")
-        if need_dx and W.shape[0] % 32:
-            raise ValueError(f"nvfp4 input gradients need out_features ({W.shape[0]}) to be a multiple of 32")
+            ctx.shape_error = f"nvfp4 weight gradients need the flattened batch ({X.shape[0]}) to be a multiple of 32"
+        elif need_dx and W.shape[0] % 32:
+            ctx.shape_error = f"nvfp4 input gradients need out_features ({W.shape[0]}) to be a multiple of 32"
+        if ctx.shape_error is not None:
+            Wc, Wsf, _, _ = F.quant_pair("nvfp4", W, True, False)
+            Xc, Xsf, _, _ = F.quant_pair("nvfp4", X, True, False)
+            ctx.layer_call = False
+            return F.gemm("nvfp4", Xc, Xsf, Wc, Wsf, b, X.dtype)
         ctx.layer_call = F.layer_call_ok("nvfp4", X, W, need_dx, need_dw) and ctx.grad_scale == 1.0
         if ctx.layer_call:      # one C call for the layer; the workspace holds the backward operands
             Y, ws = F.layer_forward("nvfp4", X, W, b, need_dx, need_dw)
@@ -74,6 +82,8 @@ class Nvfp4Matmul(torch.autograd.Function):
     @staticmethod
     @custom_bwd(device_type="cuda")
     def backward(ctx, grad_Y):
+        if getattr(ctx, "shape_error", None) is not None:
+            raise ValueError(ctx.shape_error)
         grad_Y = grad_Y.contiguous()
         grad_X = grad_W = grad_b = None
         if not ctx.fused:

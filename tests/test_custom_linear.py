@@ -155,16 +155,19 @@ def test_fused_path_equals_operator_path(cls, monkeypatch):
 @pytest.mark.parametrize("n", [48, 16, 80])
 def test_nvfp4_batch_multiple_of_16_but_not_32(n):
     """wgrad contracts over the batch, and an FP4 GEMM's K has to be a multiple of 32: a batch of
-    48 cannot train the layer.  The error comes from forward (a ValueError naming the batch), not
-    from the middle of the backward pass; with frozen parameters the same batch runs."""
+    48 cannot train the layer.  Forward runs (the reference's own tests call it with a batch of 4);
+    backward raises a ValueError naming the batch before it launches anything; with frozen
+    parameters the same batch runs forward and backward."""
     torch.manual_seed(n)
     ic, oc = 64, 96
     ref = nn.Linear(ic, oc).to(device="cuda", dtype=torch.bfloat16)
     layer = CublasltNvfp4Linear(ic, oc).to(device="cuda", dtype=torch.bfloat16)
     layer.load_state_dict(ref.state_dict())
     x = torch.randn(n, ic, device="cuda", dtype=torch.bfloat16)
+    y = layer(x)
+    assert y.shape == (n, oc) and _rel(y, ref(x)) <= 2.5e-1
     with pytest.raises(ValueError, match="multiple of 32"):
-        layer(x)
+        y.backward(torch.randn_like(y))
     layer.requires_grad_(False)
     xg = x.clone().requires_grad_(True)
     xr = x.clone().requires_grad_(True)
