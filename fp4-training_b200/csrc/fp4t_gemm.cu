@@ -1025,11 +1025,13 @@ int launch_best_width(const void* p_codes, const void* q_codes, const GemmParams
     set_error("%s: the kernel cannot be resident on this device", name);
     return FP4T_ERR_DEVICE;
   }
-  // Tile width: fewer, wider tiles unless narrow ones fill the machine better.  The time of a
-  // tile is set by the bytes it pulls in per K slab: 128 rows of P plus kBN rows of Q.
+  // Tile width: fewer, wider tiles unless narrow ones fill the machine better.  Relative time of
+  // a tile per K slab, measured on long-K products (16384 x 128 x 8192 against 16384 x 256 x 8192,
+  // one wave each: 17.2 against 19.3 us): a 128-column tile costs 0.89 of a 256-column one, not
+  // the 0.67 its operand bytes suggest (the 128 rows of P and the scale tiles do not shrink).
   const int64_t cm = ceil_div(g.m_tiles, kCtas);
-  const double k256 = (double)ceil_div(cm * ceil_div(cols, 256), c256) * (128.0 + 256.0);
-  const double k128 = (double)ceil_div(cm * ceil_div(cols, 128), c128) * (128.0 + 128.0);
+  const double k256 = (double)ceil_div(cm * ceil_div(cols, 256), c256) * 384.0;
+  const double k128 = (double)ceil_div(cm * ceil_div(cols, 128), c128) * 342.0;
   if (kCtas == 1) {
     // skinny outputs (at most 128 rows): the whole job is streaming Q once, so what matters is
     // that every SM pulls; 64-column tiles double the number of CTAs at work
