@@ -701,6 +701,22 @@ def run_single_kernel(args):
     from backend import ops
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    if args.kernel in ("layernorm_fwd", "layernorm_bwd"):
+        # the LayerNorm of the small model: 512 x 50 tokens of width 192, fp32 residual stream in,
+        # bf16 out / bf16 gradient in (29.5 and 49 MB of traffic per launch)
+        g = torch.Generator(device=dev).manual_seed(0)
+        x = torch.randn(25600, 192, device=dev, generator=g)
+        gamma = torch.ones(192, device=dev)
+        beta = torch.zeros(192, device=dev)
+        dy = torch.randn(25600, 192, device=dev, generator=g).to(torch.bfloat16)
+        _, mean, rstd = ops.layernorm_forward(x, gamma, beta, 1e-5, torch.bfloat16)
+        if args.kernel == "layernorm_fwd":
+            fn = lambda: ops.layernorm_forward(x, gamma, beta, 1e-5, torch.bfloat16)      # noqa: E731
+        else:
+            fn = lambda: ops.layernorm_backward(dy, x, mean, rstd, gamma)                  # noqa: E731
+        ms = time_loop(fn, args.steps, warm=args.warmup)
+        print(json.dumps({"kernel": args.kernel, "launches": args.steps, "ms_per_launch": ms}))
+        return
     inputs = synth_inputs(N, IC, OC, 0, dev)
     fn = kernel_closures(ops, inputs, inputs[3])[0][args.kernel]
     ms = time_loop(fn, args.steps, warm=args.warmup)
@@ -1052,7 +1068,7 @@ def main():
     ap.add_argument("--sweep-max", type=int, default=0, help="gemm_sweep: largest dimension to include (0 = all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default=None,
-                    choices=["quant_w", "quant_x", "quant_g", "fprop", "dgrad", "wgrad"],
+                    choices=["quant_w", "quant_x", "quant_g", "fprop", "dgrad", "wgrad", "layernorm_fwd", "layernorm_bwd"],
                     help="run only this kernel of the step (profiling aid); no benchmark line")
     args = ap.parse_args()
     args.steps_given = args.steps is not None
