@@ -32,9 +32,13 @@ class AttentionBlock(nn.Module):
     (models/transformer_block.py:74,95) attn_scale is 1 / dh**-0.5, i.e. the scores are
     MULTIPLIED by sqrt(dh); loss-curve parity depends on keeping that."""
 
-    def __init__(self, E, H, dropout=0.1, impl="torch", fused_norm=False, fuse_qkv=False):
+    def __init__(self, E, H, dropout=0.1, impl="torch", fused_norm=False, fuse_qkv=False, sdpa=False):
         super().__init__()
         self.fuse_qkv = fuse_qkv        # an addition: q / k / v as one quantization + one GEMM over stacked weights
+        # an addition: the attention core through torch's scaled_dot_product_attention (a library
+        # kernel, the same for every recipe) instead of the reference's matmul / softmax / dropout
+        # sequence with its layout copies; same arithmetic, the dropout mask comes from another generator
+        self.sdpa = sdpa
         assert E % H == 0, "head size is not multiple of embedding size"
         self.E, self.H, self.dh = E, H, E // H
         self.attn_scale = 1 / (self.dh ** -0.5)
@@ -55,6 +59,12 @@ class AttentionBlock(nn.Module):
         else:
             q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
         q = q.view(B, L, self.H, self.dh).transpose(1, 2)
+        if self.sdpa:
+            k = k.view(B, L, self.H, self.dh).transpose(1, 2)
+            v = v.view(B, L, self.H, self.dh).transpose(1, 2)
+            attn = F.scaled_dot_product_attention(q, k, v, dropout_p=self.dropout.p if self.training else 0.0,
+                                                  scale=self.attn_scale)
+            return residual + self.o_proj(attn.transpose(1, 2).reshape(B, L, E))
         k_t = k.view(B, L, self.H, self.dh).transpose(1, 2).transpose(-2, -1)
         v = v.view(B, L, self.H, self.dh).transpose(1, 2)
         prob = self.dropout(F.softmax((q @ k_t) * self.attn_scale, dim=-1))
@@ -63,13 +73,13 @@ class AttentionBlock(nn.Module):
 
 
 class TransformerBlock(nn.Module):
-    def __init__(self, E, F, H, dropout=0.1, impl="torch", fuse_gelu=False, fused_norm=False, fuse_qkv=False):
+    def __init__(self, E, F, H, dropout=0.1, impl="torch", fuse_gelu=False, fused_norm=False, fuse_qkv=False, sdpa=False):
         super().__init__()
         self.E, self.F, self.H, self.impl = E, F, H, impl
         self.fuse_gelu = fuse_gelu      # an addition: see forward()
         # fused_norm (an addition): the two `preln` modules run on the library's LayerNorm kernels
         # (same parameters and state dict as nn.LayerNorm)
-        self.attn = AttentionBlock(E, H, dropout, impl=impl, fused_norm=fused_norm, fuse_qkv=fuse_qkv)
+        self.attn = AttentionBlock(E, H, dropout, impl=impl, fused_norm=fused_norm, fuse_qkv=fuse_qkv, sdpa=sdpa)
         linear = LINEAR_IMPL[impl]
         self.ffn = nn.ModuleDict({
             "preln": FusedLayerNorm(E) if fused_norm else nn.LayerNorm(E),

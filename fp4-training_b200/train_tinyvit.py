@@ -32,9 +32,9 @@ from dp import GradAllReducer, broadcast_parameters  # noqa: E402
 from models import REF_IMPL, TinyViT  # noqa: E402
 
 
-def build_model(impl, depth, device, fused_norm=False, fuse_qkv=False):
+def build_model(impl, depth, device, fused_norm=False, fuse_qkv=False, sdpa=False):
     return TinyViT(img_size=28, patch_size=4, in_chans=1, num_classes=10, embed_dim=192, num_heads=3,
-                   mlp_ratio=4.0, linear_impl=impl, depth=depth, fused_norm=fused_norm, fuse_qkv=fuse_qkv).to(device)
+                   mlp_ratio=4.0, linear_impl=impl, depth=depth, fused_norm=fused_norm, fuse_qkv=fuse_qkv, sdpa=sdpa).to(device)
 
 
 def _sync(device, world):
@@ -45,7 +45,7 @@ def _sync(device, world):
 
 
 def train(impl="cublaslt_nvfp4", steps=200, warmup=5, batch=512, depth=6, seed=0, lr=1e-3, device=None, log=None,
-          fp32=False, graph=False, fused_norm=False, fuse_qkv=False):
+          fp32=False, graph=False, fused_norm=False, fuse_qkv=False, sdpa=False):
     """graph=True (CUDA only): forward + backward and the optimizer step are captured once into
     two CUDA graphs and replayed per step, with the gradient all-reduce (one NCCL call on a flat
     buffer that all `.grad` tensors are views of) between them.  The step is launch-bound at
@@ -62,7 +62,7 @@ def train(impl="cublaslt_nvfp4", steps=200, warmup=5, batch=512, depth=6, seed=0
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl" if device.type == "cuda" else "gloo")
     torch.manual_seed(seed)
-    model = build_model(impl, depth, device, fused_norm, fuse_qkv)
+    model = build_model(impl, depth, device, fused_norm, fuse_qkv, sdpa)
     broadcast_parameters(model)
     crit = nn.CrossEntropyLoss()
     torch.manual_seed(seed + 1000 * (rank + 1))        # data, dropout and rounding noise differ per rank
@@ -154,7 +154,7 @@ def train(impl="cublaslt_nvfp4", steps=200, warmup=5, batch=512, depth=6, seed=0
             for i, v in enumerate(losses):
                 f.write(json.dumps({"step": i, "loss": v}) + "\n")
     return {"impl": impl, "steps": steps, "world": world, "batch_per_gpu": batch, "depth": depth, "graph": bool(graph),
-            "fused_norm": bool(fused_norm), "fuse_qkv": bool(fuse_qkv),
+            "fused_norm": bool(fused_norm), "fuse_qkv": bool(fuse_qkv), "sdpa": bool(sdpa),
             "steps_per_s": steps / dt, "images_per_s": steps * batch * world / dt, "first_loss": losses[0],
             "last_loss": losses[-1], "losses": losses}
 
@@ -173,8 +173,9 @@ def main():
     ap.add_argument("--graph", action="store_true", help="replay the step from CUDA graphs")
     ap.add_argument("--fused-norm", action="store_true", help="LayerNorms on the library's kernels")
     ap.add_argument("--fuse-qkv", action="store_true", help="q / k / v as one quantization and one GEMM")
+    ap.add_argument("--sdpa", action="store_true", help="attention core through torch's scaled_dot_product_attention")
     a = ap.parse_args()
-    out = train(a.impl, a.steps, a.warmup, a.batch_size, a.depth, a.seed, a.lr, None, a.log, a.fp32, a.graph, a.fused_norm, a.fuse_qkv)
+    out = train(a.impl, a.steps, a.warmup, a.batch_size, a.depth, a.seed, a.lr, None, a.log, a.fp32, a.graph, a.fused_norm, a.fuse_qkv, a.sdpa)
     if int(os.environ.get("RANK", "0")) == 0:
         out["losses"] = out["losses"][:: max(1, len(out["losses"]) // 20)]
         print(json.dumps(out), flush=True)

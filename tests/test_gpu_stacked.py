@@ -78,3 +78,17 @@ def test_model_option_gives_the_same_logits():
     x = torch.rand(64, 1, 28, 28, device="cuda")
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
         assert torch.equal(a(x), b(x))
+
+
+def test_sdpa_option_matches_the_explicit_attention():
+    """sdpa=True: same attention arithmetic through torch's fused kernel (eval mode: no dropout)."""
+    from models import TinyViT
+    torch.manual_seed(0)
+    kw = dict(img_size=28, patch_size=4, embed_dim=192, num_heads=3, mlp_ratio=4.0, depth=2, linear_impl="cublaslt_nvfp4")
+    a = TinyViT(**kw).cuda().eval()
+    b = TinyViT(sdpa=True, **kw).cuda().eval()
+    b.load_state_dict(a.state_dict())
+    x = torch.rand(64, 1, 28, 28, device="cuda")
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        la, lb = a(x).float(), b(x).float()
+    assert (la - lb).abs().max() <= 0.05 * la.abs().max().clamp_min(1.0)
