@@ -453,6 +453,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # default: the library's copy-engine exchange (measured inside the step at 4 GPUs: 0.267-0.284 ms
     # against 0.29-0.30 with NCCL and 0.254 with no exchange at all); FP4T_ALLREDUCE=nccl|switch|off
     exchange = os.environ.get("FP4T_ALLREDUCE", "copy") if world > 1 else "none"
+    exchange_note = None
+    if exchange == "copy" and mg_check is not None and not mg_check.get("copy_engine_allreduce_vs_nccl_sum", {}).get("ok", False):
+        exchange, exchange_note = "nccl", "the copy-engine exchange failed its check before the timed region; NCCL used"
     if exchange == "copy":
         # reduce-scatter + all-gather on the copy engines (no SM taken from the step's kernels
         # beyond a few-MB sum); NCCL if symmetric memory cannot be set up on these GPUs
@@ -522,6 +525,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     for i in range(warm):
         hot_step(i)
     barrier()
+    if exchange in ("copy", "switch"):
+        # a wait of the library's exchange that ran out (a peer that never arrived) shows in the
+        # status word: finish the measurement on NCCL rather than not at all, and say so
+        bad = torch.tensor([int(ops.status_word(dev)[0].item())], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()) != 0:
+            exchange_note = f"the {exchange} exchange reported status {int(bad.item())} during warm-up; NCCL used"
+            if rank == 0:
+                print(f"bench: {exchange_note}", file=sys.stderr)
+            ops.status_word(dev).zero_()
+            exchange, comm_done[0], comm_done[1] = "nccl", None, None
+            for i in range(warm):
+                hot_step(i)
+            barrier()
     launches0 = dict(ops.LAUNCHES)
 
     # ---- exactly K timed steps ----
@@ -632,6 +649,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                   "copy": "fp4t reduce-scatter + all-gather on the copy engines (peer copies, one-warp "
                                           "rendezvous, shard sum), one graph launch per step on a side stream",
                                   "nccl": "NCCL on a side stream, one call per step"}.get(exchange, exchange),
+                    **({"allreduce_note": exchange_note} if exchange_note else {}),
                     "bias_grad": "fused into the dY quantizer (fp32 atomics + finishing kernel)",
                     "frac_of_nominal_fp4_peak": value / world / FP4_NOMINAL_TFLOPS},
         "sustained": {"value": world * FLOP_PER_STEP / (sus_ms_step * 1e-3) / 1e12, "unit": UNIT,
