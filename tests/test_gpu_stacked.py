@@ -81,14 +81,16 @@ def test_model_option_gives_the_same_logits():
 
 
 def test_sdpa_option_matches_the_explicit_attention():
-    """sdpa=True: same attention arithmetic through torch's fused kernel (eval mode: no dropout)."""
+    """sdpa=True: same attention arithmetic through torch's fused kernel (eval mode: no dropout).
+    Checked on unquantized fp32 linears, where nothing amplifies the last-bit differences of the
+    two softmax implementations."""
     from models import TinyViT
     torch.manual_seed(0)
-    kw = dict(img_size=28, patch_size=4, embed_dim=192, num_heads=3, mlp_ratio=4.0, depth=2, linear_impl="cublaslt_nvfp4")
+    kw = dict(img_size=28, patch_size=4, embed_dim=192, num_heads=3, mlp_ratio=4.0, depth=2, linear_impl="torch")
     a = TinyViT(**kw).cuda().eval()
     b = TinyViT(sdpa=True, **kw).cuda().eval()
     b.load_state_dict(a.state_dict())
     x = torch.rand(64, 1, 28, 28, device="cuda")
-    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-        la, lb = a(x).float(), b(x).float()
-    assert (la - lb).abs().max() <= 0.05 * la.abs().max().clamp_min(1.0)
+    with torch.no_grad():
+        la, lb = a(x), b(x)
+    assert torch.allclose(la, lb, rtol=1e-3, atol=1e-4)
