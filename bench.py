@@ -606,7 +606,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     del closures, operands
 
     # end-to-end through the module API with host buffers
-    e2e_ms, h2d, d2h = run_e2e(args, dev, rank, world)
+    e2e_ms, h2d, d2h, h2d_gbs = run_e2e(args, dev, rank, world)
     sampler.stop()
 
     t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
@@ -678,6 +678,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "comparator": comparator,
         "e2e": {"value": world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "h2d_gbs_per_rank_alone": h2d_gbs,      # the same pinned buffers copied with nothing else running, slowest rank
                 "api": "custom.CublasltNvfp4Linear forward+backward under bf16 autocast"},
         "gpu_launches": launches,
         "host_enqueue_ms_per_step": host_enqueue_ms,
@@ -806,13 +807,27 @@ def run_e2e(args, dev, rank, world):
         return total
 
     run(2)
+    # what the host side can feed: the same pinned buffers copied with nothing else running, all
+    # ranks at once (the end-to-end number is bound by this copy, so it is printed beside it)
     if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    c0 = time.perf_counter()
+    for _ in range(3):
+        start_copy(0)
+        consumed[0].record()
+    copy_stream.synchronize()
+    h2d_gbs = 3 * h2d / (time.perf_counter() - c0) / 1e9
+    if world > 1:
+        tmin = torch.tensor([h2d_gbs], device=dev, dtype=torch.float64)
+        dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        h2d_gbs = float(tmin[0])
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     run(steps)
     torch.cuda.synchronize()
-    return (time.perf_counter() - t0) * 1e3 / steps, h2d, 4
+    return (time.perf_counter() - t0) * 1e3 / steps, h2d, 4, h2d_gbs
 
 
 # --------------------------------------------------------------------------------------
