@@ -126,3 +126,71 @@ def test_training_script_runs_and_learns():
     out = train("cublaslt_nvfp4", steps=12, warmup=2, batch=64, depth=2, seed=0)
     assert out["world"] == 1 and len(out["losses"]) == 14
     assert all(v == v and v < 10 for v in out["losses"])
+
+
+def test_loss_curve_with_library_layernorm_tracks_reference_recipe(monkeypatch):
+    """fused_norm=True (the library's LayerNorm kernels) against the reference recipe on
+    nn.LayerNorm: the normalised rows differ in the last fp32 bit before their bf16 rounding, so
+    the curves track each other as closely as with torch's LayerNorm on both sides."""
+    monkeypatch.setenv("FP4T_PARITY", "1")
+    torch.manual_seed(0)
+    kw = dict(patch_size=4, embed_dim=192, num_heads=3, mlp_ratio=4.0, depth=2, linear_impl="cublaslt_nvfp4")
+    ours = TinyViT(fused_norm=True, **kw).cuda()
+    ref = TinyViT(**kw).cuda()
+    ref.load_state_dict(ours.state_dict())
+    _swap_linears(ref, OracleLinear)
+    a = _run(ours, 20, 3)
+    b = _run(ref, 20, 3)
+    diffs = [abs(x - y) for x, y in zip(a, b)]
+    assert all(v == v for v in a + b)
+    assert max(diffs) <= 0.1, (a, b)
+    assert sum(diffs) / len(diffs) <= 0.04, (a, b)
+    assert abs(a[0] - b[0]) <= 5e-3
+    from backend import ops
+    ops.check_status()
+
+
+def _run_learnable(model, steps, seed, batch=128):
+    """A task with something to learn: the label is the brightest of ten fixed image regions."""
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    torch.manual_seed(seed)
+    gen = torch.Generator(device="cuda").manual_seed(seed + 1)
+    losses = []
+    for _ in range(steps):
+        x = torch.rand(batch, 1, 28, 28, device="cuda", generator=gen)
+        y = torch.randint(0, 10, (batch,), device="cuda", generator=gen)
+        rows = torch.arange(batch, device="cuda")
+        for k in range(10):                                  # brighten region k of the images labelled k
+            sel = rows[y == k]
+            r0, c0 = 2 + 5 * (k // 5) * 2, 2 + 5 * (k % 5)
+            x[sel, :, r0:r0 + 5, c0:c0 + 5] += 1.0
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = nn.functional.cross_entropy(model(x), y)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    return losses
+
+
+def test_block_options_learn_like_the_reference_module_tree():
+    """fused_norm + fuse_qkv (+ sdpa) change kernels, not the recipe: on a learnable task the loss
+    falls at least as fast as on the reference's module tree (in-kernel stochastic rounding, so the
+    curves agree statistically, not step by step; the loss is still falling steeply at step 60, so
+    the bound is one-sided)."""
+    kw = dict(patch_size=4, embed_dim=192, num_heads=3, mlp_ratio=4.0, depth=2, linear_impl="cublaslt_nvfp4")
+    torch.manual_seed(0)
+    plain = TinyViT(**kw).cuda()
+    state = {k: v.clone() for k, v in plain.state_dict().items()}
+    curves = {"plain": _run_learnable(plain, 60, 11)}
+    for name, opts in (("fused", dict(fused_norm=True, fuse_qkv=True)),
+                       ("fused+sdpa", dict(fused_norm=True, fuse_qkv=True, sdpa=True))):
+        m = TinyViT(**kw, **opts).cuda()
+        m.load_state_dict(state)
+        curves[name] = _run_learnable(m, 60, 11)
+    tail = {k: sum(v[-10:]) / 10 for k, v in curves.items()}
+    assert tail["plain"] < 1.2, f"the task was not learned: {tail}"          # from ln(10) = 2.30
+    for name in ("fused", "fused+sdpa"):      # measured: 0.82 plain, 0.62 and 0.57 with the options
+        assert tail[name] < 1.2 and tail[name] <= tail["plain"] + 0.25, tail
+    from backend import ops
+    ops.check_status()
