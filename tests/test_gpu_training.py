@@ -79,8 +79,8 @@ def test_loss_curve_tracks_reference_recipe(monkeypatch):
 def test_loss_curve_full_configuration(monkeypatch):
     """The TinyViT configuration of the benchmark as specified: depth 6 (36 NVFP4 projections),
     batch 512, AdamW lr 1e-3, 200 steps, seed 0, against the reference recipe on identical seeds.
-    Both curves are written as JSON lines (gpurun_out/tinyvit_config4_losses.jsonl when that
-    folder can be created) and the gaps are asserted per window: the two runs differ only in
+    Both curves are written as JSON lines (tinyvit_config4_losses.jsonl in the run's output
+    folder at the repository root, when that can be created) and the gaps are asserted per window: the two runs differ only in
     fp32 accumulation order and bf16 rounding of GEMM outputs."""
     import json
     monkeypatch.setenv("FP4T_PARITY", "1")
