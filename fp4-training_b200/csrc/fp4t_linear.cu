@@ -1,6 +1,9 @@
 // One-call forward and backward of a quantized linear layer on top of the quantizer and GEMM
 // entry points: the host crosses the C ABI twice per layer and step instead of six times, and
 // every intermediate (codes, scales, column-sum scratch) lives in one caller-owned workspace.
+#include <cstdlib>
+#include <mutex>
+
 #include "fp4t_common.cuh"
 
 namespace fp4t {
@@ -46,6 +49,35 @@ BwdSections bwd_sections(int fmt, int64_t n, int64_t oc, int64_t ic) {
   s.splitk = o; o += align256(s.splitk_bytes);
   s.total = o;
   return s;
+}
+
+// A helper stream and two events per (device, caller stream): dgrad runs beside wgrad (below).
+struct SideLane {
+  int dev;
+  cudaStream_t owner;
+  cudaStream_t side;
+  cudaEvent_t fork, join;
+};
+SideLane* side_lane_for(cudaStream_t stream) {
+  static std::mutex mu;
+  static SideLane lanes[kSchedSlots];
+  static int used = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (stream == cudaStreamPerThread) return nullptr;    // one handle, a different stream per host thread
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (lanes[i].dev == dev && lanes[i].owner == stream) return &lanes[i];
+  if (used == kSchedSlots) return nullptr;
+  SideLane l{dev, stream, nullptr, nullptr, nullptr};
+  if (cudaStreamCreateWithFlags(&l.side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  lanes[used] = l;
+  return &lanes[used++];
 }
 
 }  // namespace
@@ -131,6 +163,29 @@ extern "C" int fp4t_linear_backward(int fmt, const void* g, int g_dtype, int64_t
   }
   auto gemm = fmt == 0 ? fp4t_gemm_nvfp4 : fp4t_gemm_mxfp8;
   auto gemm_splitk = fmt == 0 ? fp4t_gemm_nvfp4_splitk : fp4t_gemm_mxfp8_splitk;
+  // dgrad and wgrad depend on the quantized dY only, not on each other.  Both are persistent
+  // grids that end in a partly filled wave of tiles (wgrad of a square layer over a long batch:
+  // 3.46 waves of 74 clusters), so they are put on two streams: wgrad stays on the caller's
+  // stream -- its CTAs are resident first -- and dgrad's clusters take the SMs that wgrad's last
+  // wave leaves idle instead of waiting for the whole grid to end.  The caller's stream waits
+  // for both.  (FP4T_SERIAL_BWD=1 keeps the two GEMMs in sequence on one stream.)
+  static const bool serial = [] { const char* e = getenv("FP4T_SERIAL_BWD"); return e && e[0] == '1'; }();
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // small layers gain nothing from it: the fork and join cost about as much as their tails
+  const bool big = (double)n * (double)oc * (double)ic >= 1.0e10;
+  SideLane* lane = (dx && dw && !serial && big) ? side_lane_for(s) : nullptr;
+  if (lane != nullptr) {
+    FP4T_CUDA(cudaEventRecord(lane->fork, s));
+    FP4T_CUDA(cudaStreamWaitEvent(lane->side, lane->fork, 0));
+    rc = gemm_splitk(gtc, gtsf, fw + f.xtc, fw + f.xtsf, nullptr, dw, out_dtype, lddw, oc, ic, n,
+                     b.splitk_bytes ? bw + b.splitk : nullptr, b.splitk_bytes, status, stream);
+    int rc2 = gemm(gc, gsf, fw + f.wtc, fw + f.wtsf, nullptr, dx, out_dtype, lddx, n, ic, oc, status,
+                   reinterpret_cast<fp4t_stream_t>(lane->side));
+    // the join is made whatever the launches returned, so that the side stream never outlives the call
+    FP4T_CUDA(cudaEventRecord(lane->join, lane->side));
+    FP4T_CUDA(cudaStreamWaitEvent(s, lane->join, 0));
+    return rc != FP4T_OK ? rc : rc2;
+  }
   if (dx) {   // dX[n, ic] = dY[n, oc] . (W^T)[ic, oc]^T
     rc = gemm(gc, gsf, fw + f.wtc, fw + f.wtsf, nullptr, dx, out_dtype, lddx, n, ic, oc, status, stream);
     if (rc != FP4T_OK) return rc;
