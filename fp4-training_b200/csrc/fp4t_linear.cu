@@ -107,22 +107,44 @@ extern "C" int fp4t_linear_forward(int fmt, const void* x, int x_dtype, int64_t 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   const bool keep_wt = keep & 1, keep_xt = keep & 2;
   int rc;
+  // The two quantizers are independent persistent grids, and W's ends in a partly filled wave of
+  // tiles (4096 x 4096: 3.46 waves); for large layers X's runs on the helper stream beside it and
+  // takes the SMs that wave leaves idle.  The GEMM, on the caller's stream, waits for both.
+  static const bool serial = [] { const char* e = getenv("FP4T_SERIAL_FWD"); return e && e[0] == '1'; }();
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  SideLane* lane = (!serial && (double)n * (double)ic >= 1.6e7 && (double)oc * (double)ic >= 4.0e6) ? side_lane_for(cs) : nullptr;
+  fp4t_stream_t xstream = stream;
+  if (lane != nullptr) {
+    FP4T_CUDA(cudaEventRecord(lane->fork, cs));
+    FP4T_CUDA(cudaStreamWaitEvent(lane->side, lane->fork, 0));
+    xstream = reinterpret_cast<fp4t_stream_t>(lane->side);
+  }
+  auto join = [&]() -> int {
+    if (lane == nullptr) return FP4T_OK;
+    FP4T_CUDA(cudaEventRecord(lane->join, lane->side));
+    FP4T_CUDA(cudaStreamWaitEvent(cs, lane->join, 0));
+    return FP4T_OK;
+  };
   if (fmt == 0) {
     rc = fp4t_quantize_nvfp4(w, w_dtype, oc, ic, ldw, ws + s.wc, ws + s.wsf, keep_wt ? ws + s.wtc : nullptr,
                              keep_wt ? ws + s.wtsf : nullptr, FP4T_SR_NONE, nullptr, nullptr, 0, stream);
+    const int rc2 = fp4t_quantize_nvfp4(x, x_dtype, n, ic, ldx, ws + s.xc, ws + s.xsf, keep_xt ? ws + s.xtc : nullptr,
+                                        keep_xt ? ws + s.xtsf : nullptr, FP4T_SR_NONE, nullptr, nullptr, 0, xstream);
+    const int rc3 = join();
     if (rc != FP4T_OK) return rc;
-    rc = fp4t_quantize_nvfp4(x, x_dtype, n, ic, ldx, ws + s.xc, ws + s.xsf, keep_xt ? ws + s.xtc : nullptr,
-                             keep_xt ? ws + s.xtsf : nullptr, FP4T_SR_NONE, nullptr, nullptr, 0, stream);
-    if (rc != FP4T_OK) return rc;
+    if (rc2 != FP4T_OK) return rc2;
+    if (rc3 != FP4T_OK) return rc3;
     return fp4t_gemm_nvfp4(ws + s.xc, ws + s.xsf, ws + s.wc, ws + s.wsf, bias_bf16, y, y_dtype, ldy, n, oc, ic, status,
                            stream);
   }
   rc = fp4t_quantize_mxfp8(w, w_dtype, oc, ic, ldw, ws + s.wc, ws + s.wsf, keep_wt ? ws + s.wtc : nullptr,
                            keep_wt ? ws + s.wtsf : nullptr, stream);
+  const int rc2 = fp4t_quantize_mxfp8(x, x_dtype, n, ic, ldx, ws + s.xc, ws + s.xsf, keep_xt ? ws + s.xtc : nullptr,
+                                      keep_xt ? ws + s.xtsf : nullptr, xstream);
+  const int rc3 = join();
   if (rc != FP4T_OK) return rc;
-  rc = fp4t_quantize_mxfp8(x, x_dtype, n, ic, ldx, ws + s.xc, ws + s.xsf, keep_xt ? ws + s.xtc : nullptr,
-                           keep_xt ? ws + s.xtsf : nullptr, stream);
-  if (rc != FP4T_OK) return rc;
+  if (rc2 != FP4T_OK) return rc2;
+  if (rc3 != FP4T_OK) return rc3;
   return fp4t_gemm_mxfp8(ws + s.xc, ws + s.xsf, ws + s.wc, ws + s.wsf, bias_bf16, y, y_dtype, ldy, n, oc, ic, status,
                          stream);
 }

@@ -339,10 +339,11 @@ FP4T_API int fp4t_gemm_mxfp8_splitk(const void* p_codes, const void* p_sf, const
  * and computes any of dX [n, ic] = dY W, dW [oc, ic] = dY^T X and db [oc] = column sums of dY
  * (null pointers skip an output) from the forward workspace and a second workspace of
  * fp4t_linear_backward_workspace_bytes(fmt, n, oc, ic) bytes (it includes the fp32 slices of a
- * split-K wgrad when dW is small).  Outputs are written in out_dtype.  For large layers dX is
- * computed on a helper stream the library keeps per (device, caller stream), beside dW, and
- * `stream` waits for it before the call's work ends in stream order: to the caller everything
- * is ordered on `stream` as usual (also under graph capture).
+ * split-K wgrad when dW is small).  Outputs are written in out_dtype.  For large layers part of
+ * the work (X's quantizer in forward, dX's GEMM in backward) runs on a helper stream the library
+ * keeps per (device, caller stream), beside its independent sibling, and `stream` waits for it
+ * before the call's work ends in stream order: to the caller everything is ordered on `stream`
+ * as usual (also under graph capture).
  * Shape requirements are those of the quantizer and GEMM entry points (ic, oc multiples of the
  * block size; n % 32 == 0 for the transposed operands).
  *
