@@ -437,6 +437,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         from backend import _lib as _l
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         _l.lib().fp4t_set_sm_limit(sms - reserve)
+    # One GPU, nothing else on it: let large layers run the independent halves of a layer call on
+    # two streams.  Off with a gradient exchange in flight (its rendezvous kernels wait for other
+    # GPUs, and work queued behind them on a shared hardware queue would wait too).
+    from backend import _lib as _l0
+    _l0.lib().fp4t_set_layer_concurrency(1 if world == 1 else 0)
     peaks = measured_peaks()
     mg_check = multi_gpu_check(ops, dev, rank, world) if world > 1 else None
 
@@ -651,6 +656,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                   "nccl": "NCCL on a side stream, one call per step"}.get(exchange, exchange),
                     **({"allreduce_note": exchange_note} if exchange_note else {}),
                     "bias_grad": "fused into the dY quantizer (fp32 atomics + finishing kernel)",
+                    "layer_concurrency": ("on: X's quantizer beside W's, dgrad beside wgrad (two streams, joined)"
+                                          if world == 1 else "off (a gradient exchange is in flight)"),
                     "frac_of_nominal_fp4_peak": value / world / FP4_NOMINAL_TFLOPS},
         "sustained": {"value": world * FLOP_PER_STEP / (sus_ms_step * 1e-3) / 1e12, "unit": UNIT,
                       "ms_per_step": sus_ms_step, "steps": blocks * args.steps, "seconds": sus_ms_total * 1e-3,

@@ -29,6 +29,7 @@ _SIGNATURES = {
     "fp4t_set_sm_limit": (ctypes.c_int, [ctypes.c_int]),
     "fp4t_set_seed_offset_word": (ctypes.c_int, [_c_vp]),
     "fp4t_set_wait_timeout_ns": (ctypes.c_int, [ctypes.c_uint64]),
+    "fp4t_set_layer_concurrency": (ctypes.c_int, [ctypes.c_int]),
     "fp4t_reset_tile_counters": (ctypes.c_int, [ctypes.c_void_p]),
     "fp4t_allreduce_sum_bf16_multimem": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
                                                        ctypes.c_int, ctypes.c_int64, ctypes.c_uint32, ctypes.c_int,

@@ -1,6 +1,7 @@
 // One-call forward and backward of a quantized linear layer on top of the quantizer and GEMM
 // entry points: the host crosses the C ABI twice per layer and step instead of six times, and
 // every intermediate (codes, scales, column-sum scratch) lives in one caller-owned workspace.
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -49,6 +50,24 @@ BwdSections bwd_sections(int fmt, int64_t n, int64_t oc, int64_t ic) {
   s.splitk = o; o += align256(s.splitk_bytes);
   s.total = o;
   return s;
+}
+
+// Whether large layers run the independent halves of a call on two streams (below).  Off unless
+// asked for (fp4t_set_layer_concurrency, or FP4T_CONCURRENT_LAYER=1 in the environment): it pays
+// when the caller's stream has the GPU to itself (0.2470 -> 0.2432 ms per step at 8192 x 4096 x
+// 4096), and it must stay off next to kernels that wait for another GPU -- the rendezvous of the
+// gradient exchange: streams share a small number of hardware queues, a kernel that waits holds
+// its queue, and work of the helper stream queued behind it waits with it (measured on two GPUs:
+// 0.258 -> 0.300 ms per step, and runs that did not finish in time).
+std::atomic<int> g_layer_concurrency{-1};
+bool layer_concurrency() {
+  int v = g_layer_concurrency.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* e = getenv("FP4T_CONCURRENT_LAYER");
+    v = (e && e[0] == '1') ? 1 : 0;
+    g_layer_concurrency.store(v, std::memory_order_relaxed);
+  }
+  return v == 1;
 }
 
 // A helper stream and two events per (device, caller stream): dgrad runs beside wgrad (below).
@@ -108,11 +127,11 @@ extern "C" int fp4t_linear_forward(int fmt, const void* x, int x_dtype, int64_t 
   const bool keep_wt = keep & 1, keep_xt = keep & 2;
   int rc;
   // The two quantizers are independent persistent grids, and W's ends in a partly filled wave of
-  // tiles (4096 x 4096: 3.46 waves); for large layers X's runs on the helper stream beside it and
-  // takes the SMs that wave leaves idle.  The GEMM, on the caller's stream, waits for both.
-  static const bool serial = [] { const char* e = getenv("FP4T_SERIAL_FWD"); return e && e[0] == '1'; }();
+  // tiles (4096 x 4096: 3.46 waves); for large layers, and with layer concurrency switched on, X's
+  // runs on the helper stream beside it and takes the SMs that wave leaves idle.  The GEMM, on the
+  // caller's stream, waits for both.
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
-  SideLane* lane = (!serial && (double)n * (double)ic >= 1.6e7 && (double)oc * (double)ic >= 4.0e6) ? side_lane_for(cs) : nullptr;
+  SideLane* lane = (layer_concurrency() && (double)n * (double)ic >= 1.6e7 && (double)oc * (double)ic >= 4.0e6) ? side_lane_for(cs) : nullptr;
   fp4t_stream_t xstream = stream;
   if (lane != nullptr) {
     FP4T_CUDA(cudaEventRecord(lane->fork, cs));
@@ -190,12 +209,11 @@ extern "C" int fp4t_linear_backward(int fmt, const void* g, int g_dtype, int64_t
   // 3.46 waves of 74 clusters), so they are put on two streams: wgrad stays on the caller's
   // stream -- its CTAs are resident first -- and dgrad's clusters take the SMs that wgrad's last
   // wave leaves idle instead of waiting for the whole grid to end.  The caller's stream waits
-  // for both.  (FP4T_SERIAL_BWD=1 keeps the two GEMMs in sequence on one stream.)
-  static const bool serial = [] { const char* e = getenv("FP4T_SERIAL_BWD"); return e && e[0] == '1'; }();
+  // for both.  Only when layer concurrency is switched on (see layer_concurrency above).
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // small layers gain nothing from it: the fork and join cost about as much as their tails
   const bool big = (double)n * (double)oc * (double)ic >= 1.0e10;
-  SideLane* lane = (dx && dw && !serial && big) ? side_lane_for(s) : nullptr;
+  SideLane* lane = (dx && dw && layer_concurrency() && big) ? side_lane_for(s) : nullptr;
   if (lane != nullptr) {
     FP4T_CUDA(cudaEventRecord(lane->fork, s));
     FP4T_CUDA(cudaStreamWaitEvent(lane->side, lane->fork, 0));
@@ -217,5 +235,10 @@ extern "C" int fp4t_linear_backward(int fmt, const void* g, int g_dtype, int64_t
                      b.splitk_bytes ? bw + b.splitk : nullptr, b.splitk_bytes, status, stream);
     if (rc != FP4T_OK) return rc;
   }
+  return FP4T_OK;
+}
+
+extern "C" int fp4t_set_layer_concurrency(int on) {
+  g_layer_concurrency.store(on ? 1 : 0, std::memory_order_relaxed);
   return FP4T_OK;
 }

@@ -339,17 +339,23 @@ FP4T_API int fp4t_gemm_mxfp8_splitk(const void* p_codes, const void* p_sf, const
  * and computes any of dX [n, ic] = dY W, dW [oc, ic] = dY^T X and db [oc] = column sums of dY
  * (null pointers skip an output) from the forward workspace and a second workspace of
  * fp4t_linear_backward_workspace_bytes(fmt, n, oc, ic) bytes (it includes the fp32 slices of a
- * split-K wgrad when dW is small).  Outputs are written in out_dtype.  For large layers part of
- * the work (X's quantizer in forward, dX's GEMM in backward) runs on a helper stream the library
- * keeps per (device, caller stream), beside its independent sibling, and `stream` waits for it
- * before the call's work ends in stream order: to the caller everything is ordered on `stream`
- * as usual (also under graph capture).
+ * split-K wgrad when dW is small).  Outputs are written in out_dtype.
+ * fp4t_set_layer_concurrency(1) (or FP4T_CONCURRENT_LAYER=1 in the environment; default off)
+ * lets large layers run part of a call (X's quantizer in forward, dX's GEMM in backward) on a
+ * helper stream the library keeps per (device, caller stream), beside its independent sibling;
+ * `stream` waits for it before the call's work ends in stream order, so to the caller
+ * everything is ordered on `stream` as usual (also under graph capture).  It fills the partly
+ * filled last wave of tiles of the sibling kernel (about 2 % of a step at 8192 x 4096 x 4096).
+ * Keep it off while kernels that wait for another GPU (fp4t_rank_meet,
+ * fp4t_allreduce_sum_bf16_multimem) can be in flight on the same device: work of the helper
+ * stream can be queued behind such a kernel in a hardware queue the two streams share.
  * Shape requirements are those of the quantizer and GEMM entry points (ic, oc multiples of the
  * block size; n % 32 == 0 for the transposed operands).
  *
  * Replaces the bodies of Nvfp4Matmul.forward / .backward (custom/linear/nvfp4.py:25-90) and
  * Mxfp8MatMul.forward / .backward (custom/linear/mxfp8.py:27-85).
  */
+FP4T_API int fp4t_set_layer_concurrency(int on);
 FP4T_API int64_t fp4t_linear_workspace_bytes(int fmt, int64_t n, int64_t ic, int64_t oc);
 FP4T_API int64_t fp4t_linear_backward_workspace_bytes(int fmt, int64_t n, int64_t oc, int64_t ic);
 FP4T_API int fp4t_linear_forward(int fmt, const void* x, int x_dtype, int64_t n, int64_t ic, int64_t ldx,
