@@ -80,3 +80,38 @@ def test_vit_train_step_cuda(linear_impl):
     assert losses[-1] < losses[0]            # memorising one batch must reduce the loss
     from backend import ops
     ops.check_status()
+
+
+def test_block_options_keep_the_module_tree():
+    """fused_norm / fuse_qkv / sdpa / fuse_gelu change kernels, not parameters: the state dict of a
+    model built with them loads into the reference's module tree and back."""
+    from custom import FusedLayerNorm
+    plain = TinyViT(embed_dim=64, num_heads=4, depth=2, linear_impl="cublaslt_nvfp4")
+    opts = TinyViT(embed_dim=64, num_heads=4, depth=2, linear_impl="cublaslt_nvfp4", fused_norm=True, fuse_qkv=True,
+                   sdpa=True, fuse_gelu=True)
+    assert list(plain.state_dict().keys()) == list(opts.state_dict().keys())
+    opts.load_state_dict(plain.state_dict())
+    plain.load_state_dict(opts.state_dict())
+    blk = opts.encoder[0]
+    assert isinstance(blk.attn.preln, FusedLayerNorm) and isinstance(blk.ffn["preln"], FusedLayerNorm)
+    assert isinstance(blk.attn.preln, nn.LayerNorm)                  # a subclass: isinstance checks of callers keep working
+    assert blk.attn.fuse_qkv and blk.attn.sdpa and blk.fuse_gelu
+
+
+def test_library_layernorm_has_no_cpu_path():
+    from custom import FusedLayerNorm
+    ln = FusedLayerNorm(64)
+    with pytest.raises(NotImplementedError):
+        ln(torch.randn(4, 64))
+    with pytest.raises(ValueError):
+        FusedLayerNorm((8, 64))                                      # last dimension only
+
+
+def test_options_with_torch_linears_run_on_cpu_where_they_can():
+    """fuse_qkv needs a quantized layer class and is ignored for nn.Linear; sdpa is plain torch."""
+    blk = TransformerBlock(E=64, F=128, H=4, impl="torch", fuse_qkv=True, sdpa=True).eval()
+    ref = TransformerBlock(E=64, F=128, H=4, impl="torch").eval()
+    ref.load_state_dict(blk.state_dict())
+    x = torch.randn(4, 10, 64)
+    with torch.no_grad():
+        assert torch.allclose(blk(x), ref(x), rtol=1e-4, atol=1e-5)
