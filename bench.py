@@ -743,6 +743,20 @@ def run_single_kernel(args):
         ms = time_loop(fn, args.steps, warm=args.warmup)
         print(json.dumps({"kernel": args.kernel, "launches": args.steps, "ms_per_launch": ms}))
         return
+    if args.kernel == "gemm_short_k":
+        # an output-bound product of the small model: 25600 x 768 x 192 (one K stage per tile, 39 MB
+        # of bf16 output), the shape the eight-warp epilogue form exists for
+        g = torch.Generator(device=dev).manual_seed(0)
+        a = torch.randn(25600, 192, device=dev, generator=g).to(torch.bfloat16)
+        b = (torch.randn(768, 192, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        ac, asf, _, _ = ops.quantize_nvfp4(a)
+        bc, bsf, _, _ = ops.quantize_nvfp4(b)
+        out = torch.empty(25600, 768, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.gemm_nvfp4(ac, asf, bc, bsf, None, torch.bfloat16, out=out)      # noqa: E731
+        ms = time_loop(fn, args.steps, warm=args.warmup)
+        ops.check_status(dev)
+        print(json.dumps({"kernel": args.kernel, "launches": args.steps, "ms_per_launch": ms}))
+        return
     inputs = synth_inputs(N, IC, OC, 0, dev)
     fn = kernel_closures(ops, inputs, inputs[3])[0][args.kernel]
     ms = time_loop(fn, args.steps, warm=args.warmup)
@@ -1117,7 +1131,8 @@ def main():
     ap.add_argument("--sweep-max", type=int, default=0, help="gemm_sweep: largest dimension to include (0 = all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default=None,
-                    choices=["quant_w", "quant_x", "quant_g", "fprop", "dgrad", "wgrad", "layernorm_fwd", "layernorm_bwd"],
+                    choices=["quant_w", "quant_x", "quant_g", "fprop", "dgrad", "wgrad", "layernorm_fwd", "layernorm_bwd",
+                             "gemm_short_k"],
                     help="run only this kernel of the step (profiling aid); no benchmark line")
     args = ap.parse_args()
     args.steps_given = args.steps is not None
