@@ -514,6 +514,13 @@ gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_
   const int cluster_id = blockIdx.x / kCtas;
   const int num_clusters = gridDim.x / kCtas;
 
+  if (threadIdx.x == 32) {   // the descriptors are kernel parameters: their fetch can run under the set-up below
+    tma_prefetch_map(&map_p);
+    tma_prefetch_map(&map_q);
+    tma_prefetch_map(&map_psf);
+    tma_prefetch_map(&map_qsf);
+    if (g.tma_ok) tma_prefetch_map(&map_d);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);      // the leader's producer arms it with the bytes of ALL CTAs

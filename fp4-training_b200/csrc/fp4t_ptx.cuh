@@ -101,6 +101,11 @@ static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t par
   }
   return true;
 }
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first use, so
+// that the first copy does not pay for fetching it.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

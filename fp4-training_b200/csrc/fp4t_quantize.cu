@@ -396,6 +396,7 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p, 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   pdl_launch_dependents();
+  if (tid == kQComputeThreads) tma_prefetch_map(&map_x);   // a kernel parameter: fetched under the set-up
   if (kFmt == kNvfp4 && tid < 128) scale_tab[tid] = make_float2(kScaleTable.v[tid].s, kScaleTable.v[tid].r);
   if (tid == 0) {
     for (int s = 0; s < kQStages; ++s) {
